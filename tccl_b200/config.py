@@ -1,0 +1,47 @@
+"""Library configuration: a small dataclass with environment overrides.
+
+The reference hard-codes its constants inside each wrapper (24 CTAs, 16 warps,
+world size 8: ``triton_all_gather.py:67-70``,
+``triton_double_tree_allreduce.py:254,356``); here they are one object that
+every rank must set identically (grid sizes derive from it and the device
+barriers pair CTAs by index).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass, fields
+
+
+def _env(name, default, cast):
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    if cast is bool:
+        return v not in ("0", "false", "False", "no")
+    return cast(v)
+
+
+@dataclass
+class Config:
+    timeout_ms: float = 5000.0        # bound of every device-side wait
+    max_ctas: int = 0                 # CTAs per collective; 0 = one per SM
+    block: int = 512                  # threads per CTA of the data collectives
+    stage_mb: int = 128               # symmetric staging area per rank
+    disable_nvls: bool = False        # never pick a multimem variant
+    nvls_barrier: bool = False        # barrier flavour used inside data kernels
+    force_variant: str = ""           # e.g. "oneshot_p2p"; empty = size-based choice
+    oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
+    tree_chunk_bytes: int = 512 * 1024    # double-tree: bytes per chunk (per tree)
+    tree_ctas: int = 16                   # double-tree: CTAs per (tree, direction)
+    debug: bool = False
+
+    @classmethod
+    def from_env(cls) -> "Config":
+        c = cls()
+        for f in fields(cls):
+            setattr(c, f.name, _env("TCCL_" + f.name.upper(), getattr(c, f.name), type(getattr(c, f.name))))
+        return c
+
+    @property
+    def timeout_ns(self) -> int:
+        return int(self.timeout_ms * 1e6)

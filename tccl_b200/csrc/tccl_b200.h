@@ -1,0 +1,144 @@
+/*
+ * C ABI of libtccl_b200: hand-written sm_100a collectives over peer-mapped
+ * (symmetric) memory.  Everything here is plain C so that the library can be
+ * loaded with ctypes / dlopen and carries no dependency on libtorch.
+ *
+ * Conventions
+ *  - Every launcher enqueues exactly one kernel on `stream` and returns the
+ *    cudaError_t of the launch (0 = success) or a negative TCCL_E* code for an
+ *    argument the launcher rejects.  Nothing synchronises the host.
+ *  - "real" mode (n_emu == 0): `comm` / `args` point to ONE struct in host
+ *    memory describing the calling rank.
+ *  - "emulated" mode (n_emu == W >= 1): `comm` / `args` point to arrays of W
+ *    structs in DEVICE memory; one cooperative launch with gridDim.y == W runs
+ *    all W ranks on the current GPU (blockIdx.y is the rank).  This is how the
+ *    multi-rank protocols are exercised on a single GPU.
+ *  - Device-side waits are bounded by `timeout_ns`; a wait that runs out
+ *    records a status (see tccl_status_word) and the kernel returns.
+ */
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TCCL_MAX_WORLD 8
+
+/* flag-region layout (in 32-bit words, per rank); the region is zeroed by reset */
+#define TCCL_MAX_BLOCKS 1024                                     /* barrier rows */
+#define TCCL_FLAG_BAR 0                                          /* [block][src]          */
+#define TCCL_FLAG_MCBAR (TCCL_FLAG_BAR + TCCL_MAX_BLOCKS * TCCL_MAX_WORLD) /* [block]     */
+#define TCCL_FLAG_TREE_UP (TCCL_FLAG_MCBAR + TCCL_MAX_BLOCKS)    /* [tree][cta][2 slots]  */
+#define TCCL_TREE_MAX_CTAS 128
+#define TCCL_FLAG_TREE_DOWN (TCCL_FLAG_TREE_UP + 2 * TCCL_TREE_MAX_CTAS * 2) /* [tree][cta] */
+#define TCCL_FLAG_TILE (TCCL_FLAG_TREE_DOWN + 2 * TCCL_TREE_MAX_CTAS)  /* [src][tile] GEMM */
+#define TCCL_MAX_TILES 4096
+#define TCCL_FLAG_LL (TCCL_FLAG_TILE + TCCL_MAX_WORLD * TCCL_MAX_TILES) /* misc / p2p */
+#define TCCL_FLAG_WORDS (TCCL_FLAG_LL + 1024)
+
+/* local (non peer-visible) state, in 32-bit words */
+#define TCCL_LOCAL_EPOCH 0                                       /* [block] p2p barrier   */
+#define TCCL_LOCAL_MCEPOCH (TCCL_LOCAL_EPOCH + TCCL_MAX_BLOCKS)  /* [block] nvls barrier  */
+#define TCCL_LOCAL_STATUS (TCCL_LOCAL_MCEPOCH + TCCL_MAX_BLOCKS) /* tccl_status_word      */
+#define TCCL_LOCAL_TILE_EPOCH (TCCL_LOCAL_STATUS + 16)           /* 1 word: tile epoch    */
+#define TCCL_LOCAL_SCHED (TCCL_LOCAL_TILE_EPOCH + 1)             /* scheduler counters    */
+#define TCCL_LOCAL_WORDS (TCCL_LOCAL_SCHED + 63)
+
+enum tccl_status_word {
+  TCCL_ST_CODE = 0,   /* 0 = ok, else tccl_error */
+  TCCL_ST_BLOCK = 1,  /* blockIdx.x of the first waiter that gave up */
+  TCCL_ST_PEER = 2,   /* peer rank it was waiting for */
+  TCCL_ST_WHERE = 3,  /* tccl_where */
+  TCCL_ST_SEEN = 4,   /* flag value last seen */
+  TCCL_ST_WANT = 5,   /* flag value waited for */
+  TCCL_ST_ABORT = 6,  /* non-zero: all further waits of this rank return at once */
+  TCCL_ST_WORDS = 16
+};
+
+enum tccl_error { TCCL_OK = 0, TCCL_TIMEOUT = 1, TCCL_BAD_INDEX = 2 };
+enum tccl_where {
+  TCCL_W_BARRIER = 1, TCCL_W_MCBARRIER = 2, TCCL_W_CAS_SEND = 3, TCCL_W_CAS_WAIT = 4,
+  TCCL_W_TREE_UP = 5, TCCL_W_TREE_DOWN = 6, TCCL_W_TILE = 7, TCCL_W_SIGNAL = 8,
+  TCCL_W_MBAR = 9
+};
+
+/* launcher-side argument errors (returned negated) */
+enum tccl_arg_error { TCCL_EINVAL = 1000, TCCL_EDTYPE = 1001, TCCL_EALIGN = 1002, TCCL_ESIZE = 1003 };
+
+enum tccl_dtype { TCCL_BF16 = 0, TCCL_F32 = 1, TCCL_F16 = 2 };
+
+/* One rank's view of the communicator.  All pointers are device addresses. */
+typedef struct tccl_comm {
+  int32_t world;
+  int32_t rank;
+  uint32_t* flags[TCCL_MAX_WORLD]; /* every rank's flag region, peer-mapped */
+  uint32_t* mc_flags;              /* multicast alias of the flag region, or NULL */
+  uint32_t* local;                 /* this rank's private state (TCCL_LOCAL_*) */
+  char* stage[TCCL_MAX_WORLD];     /* every rank's staging area, peer-mapped */
+  char* mc_stage;                  /* multicast alias of the staging area, or NULL */
+  uint64_t stage_bytes;
+  uint64_t timeout_ns;
+} tccl_comm;
+
+/* Arguments shared by the data collectives. */
+typedef struct tccl_coll_args {
+  const void* in[TCCL_MAX_WORLD]; /* every rank's input (peer-mapped, view offset applied) */
+  void* mc_in;                    /* multicast alias of the input, or NULL */
+  void* out;                      /* local output (may be NULL for in-place variants) */
+  void* out_peer[TCCL_MAX_WORLD]; /* every rank's output when it is symmetric, else unused */
+  void* mc_out;                   /* multicast alias of the symmetric output, or NULL */
+  uint64_t numel;                 /* elements of the per-rank input */
+  int32_t dtype;                  /* tccl_dtype */
+  int32_t flags;                  /* TCCL_F_* */
+} tccl_coll_args;
+
+#define TCCL_F_NO_EXIT_BARRIER 1 /* caller guarantees inputs stay untouched until peers are done */
+#define TCCL_F_NO_ENTRY_BARRIER 2
+#define TCCL_F_NVLS_BARRIER 4    /* use the multimem.red barrier flavour */
+
+typedef struct tccl_launch {
+  int32_t grid;    /* CTAs per rank */
+  int32_t block;   /* threads per CTA */
+  int32_t n_emu;   /* 0 = real, W = emulate W ranks on this GPU */
+  int32_t meta;    /* emulated mode only: tccl_dtype of the (device-resident) args */
+  void* stream;    /* cudaStream_t */
+} tccl_launch;
+
+int tccl_version(void);
+const char* tccl_error_string(int code);
+int tccl_num_sms(void);
+/* occupancy-limited CTAs per SM for kernel `name` at `block` threads (0 if unknown) */
+int tccl_max_ctas_per_sm(const char* name, int block);
+
+/* ---- barriers -------------------------------------------------------- */
+typedef struct tccl_barrier_args {
+  int32_t rounds; /* barrier rounds to run back to back inside one launch */
+} tccl_barrier_args;
+typedef struct tccl_pads_args {
+  uint32_t* pads[TCCL_MAX_WORLD]; /* every rank's signal pad, peer-mapped, laid out [block][world] */
+} tccl_pads_args;
+/* epoch barrier on the library's own flag region, by posted stores to every peer */
+int tccl_barrier_p2p(const tccl_comm*, const tccl_barrier_args*, const tccl_launch*);
+/* same, one multimem.red through the switch instead of W stores (needs comm->mc_flags) */
+int tccl_barrier_nvls(const tccl_comm*, const tccl_barrier_args*, const tccl_launch*);
+/* self-resetting CAS barrier on caller-provided signal pads (the layout of torch
+ * symmetric memory's signal pads) */
+int tccl_barrier_cas(const tccl_comm*, const tccl_pads_args*, const tccl_launch*);
+/* waits for a flag that nothing sets: exercises the timeout path (tests only) */
+int tccl_wait_never(const tccl_comm*, const tccl_barrier_args*, const tccl_launch*);
+
+/* ---- data collectives ------------------------------------------------- */
+int tccl_allreduce_oneshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allreduce_oneshot_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allreduce_twoshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allreduce_twoshot_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allgather_pull_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allgather_push_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allgather_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_reducescatter_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_reducescatter_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,99 @@
+"""In-tree build of ``libtccl_b200.so`` with nvcc for sm_100a.
+
+Every ``csrc/*.cu`` is compiled to an object under ``tccl_b200/_build`` and the
+objects are linked into ``tccl_b200/_lib/libtccl_b200.so`` (static cudart, no
+libtorch).  A source is recompiled when it, any header beside it, or the flag
+set changed.  nvcc cross-compiles without a GPU.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent.parent
+CSRC = PKG / "csrc"
+BUILD = PKG / "_build"
+LIBDIR = PKG / "_lib"
+LIB = LIBDIR / "libtccl_b200.so"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC",
+    "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("TCCL_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found (set TCCL_NVCC)")
+
+
+def _digest(paths, extra: str) -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def sources():
+    return sorted(CSRC.glob("*.cu"))
+
+
+def headers():
+    return sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
+
+
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
+    """Compile what is stale and link; returns the path of the shared library."""
+    nvcc = _nvcc()
+    BUILD.mkdir(exist_ok=True)
+    LIBDIR.mkdir(exist_ok=True)
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+    hdr = headers()
+    jobs = []
+    objs = []
+    for src in sources():
+        obj = BUILD / (src.stem + ".o")
+        stamp = BUILD / (src.stem + ".sha")
+        dig = _digest([src] + hdr, " ".join(flags))
+        objs.append(obj)
+        if force or not obj.exists() or not stamp.exists() or stamp.read_text() != dig:
+            jobs.append((src, obj, stamp, dig))
+
+    def compile_one(job):
+        src, obj, stamp, dig = job
+        cmd = [nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stdout}\n{r.stderr}")
+        stamp.write_text(dig)
+        return src.name, r.stderr
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for name, err in ex.map(compile_one, jobs):
+                if verbose or ptxas_info:
+                    print(f"[tccl_b200.build] compiled {name}", file=sys.stderr)
+                    if ptxas_info:
+                        print(err, file=sys.stderr)
+    if jobs or not LIB.exists():
+        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        if verbose:
+            print(f"[tccl_b200.build] linked {LIB}", file=sys.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)

@@ -1,0 +1,138 @@
+"""ctypes binding of ``libtccl_b200.so``.
+
+The structs mirror ``csrc/tccl_b200.h``; the numeric constants (flag-region
+layout, status words, error codes) are parsed out of that header so that the
+Python side cannot drift from the device code.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+from pathlib import Path
+from typing import Dict
+
+import torch
+
+PKG = Path(__file__).resolve().parent.parent
+HEADER = PKG / "csrc" / "tccl_b200.h"
+LIB_PATH = PKG / "_lib" / "libtccl_b200.so"
+
+
+def _parse_header(path: Path) -> Dict[str, int]:
+    text = re.sub(r"/\*.*?\*/", "", path.read_text(), flags=re.S)
+    consts: Dict[str, int] = {}
+    for m in re.finditer(r"^#define\s+(TCCL_\w+)\s+(.+)$", text, flags=re.M):
+        name, expr = m.group(1), m.group(2).strip()
+        try:
+            consts[name] = int(eval(expr, {"__builtins__": {}}, consts))
+        except Exception:
+            pass
+    for m in re.finditer(r"enum\s+\w+\s*\{(.*?)\}", text, flags=re.S):
+        nxt = 0
+        for item in m.group(1).split(","):
+            item = item.strip()
+            if not item:
+                continue
+            if "=" in item:
+                k, v = (s.strip() for s in item.split("=", 1))
+                nxt = int(eval(v, {"__builtins__": {}}, consts))
+            else:
+                k = item
+            consts[k] = nxt
+            nxt += 1
+    return consts
+
+
+K = _parse_header(HEADER)
+MAX_WORLD = K["TCCL_MAX_WORLD"]
+
+
+class Comm(C.Structure):
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("flags", C.c_uint64 * MAX_WORLD),
+        ("mc_flags", C.c_uint64),
+        ("local", C.c_uint64),
+        ("stage", C.c_uint64 * MAX_WORLD),
+        ("mc_stage", C.c_uint64),
+        ("stage_bytes", C.c_uint64),
+        ("timeout_ns", C.c_uint64),
+    ]
+
+
+class CollArgs(C.Structure):
+    _fields_ = [
+        ("inp", C.c_uint64 * MAX_WORLD),
+        ("mc_in", C.c_uint64),
+        ("out", C.c_uint64),
+        ("out_peer", C.c_uint64 * MAX_WORLD),
+        ("mc_out", C.c_uint64),
+        ("numel", C.c_uint64),
+        ("dtype", C.c_int32),
+        ("flags", C.c_int32),
+    ]
+
+
+class BarrierArgs(C.Structure):
+    _fields_ = [("rounds", C.c_int32)]
+
+
+class PadsArgs(C.Structure):
+    _fields_ = [("pads", C.c_uint64 * MAX_WORLD)]
+
+
+class Launch(C.Structure):
+    _fields_ = [
+        ("grid", C.c_int32),
+        ("block", C.c_int32),
+        ("n_emu", C.c_int32),
+        ("meta", C.c_int32),
+        ("stream", C.c_void_p),
+    ]
+
+
+DTYPES = {torch.bfloat16: K["TCCL_BF16"], torch.float32: K["TCCL_F32"], torch.float16: K["TCCL_F16"]}
+
+_lib = None
+
+
+class TcclError(RuntimeError):
+    """A launcher rejected its arguments or CUDA refused the launch."""
+
+
+class TcclTimeout(RuntimeError):
+    """A device-side wait ran out; carries the decoded status words."""
+
+    def __init__(self, status: dict):
+        super().__init__(f"device wait gave up: {status}")
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    """Load the shared library (building it first if it is missing and nvcc is
+    there).  On a machine with a GPU a missing library is an error, never a
+    silent fallback."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists() or os.environ.get("TCCL_REBUILD") == "1":
+        from . import build as _build
+
+        _build.build()
+    _lib = C.CDLL(str(LIB_PATH))
+    _lib.tccl_error_string.restype = C.c_char_p
+    _lib.tccl_error_string.argtypes = [C.c_int]
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().tccl_error_string(code).decode()
+        raise TcclError(f"{what}: {msg} (code {code})")
+
+
+def call(name: str, comm_ptr, args_ptr, launch: Launch) -> None:
+    fn = getattr(lib(), name)
+    check(fn(comm_ptr, args_ptr, C.byref(launch)), name)

@@ -1,0 +1,145 @@
+"""Multi-GPU correctness worker: one process per GPU, started by
+``torch.distributed.run`` from tests/test_multigpu.py (or by hand).  Every rank
+regenerates all ranks' seeded inputs on the CPU, so each rank checks its own
+result against an fp32 host sum without extra communication.  Prints one JSON
+line per rank-0 summary and exits non-zero on any failure."""
+import json
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import tccl_b200 as tccl  # noqa: E402
+
+TOL = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11, torch.float32: 1e-6}
+
+
+def seeded(n, dtype, seed, kind="normal"):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    t = torch.randn(n, generator=g) if kind == "normal" else torch.rand(n, generator=g) * 2 - 1
+    return t.to(dtype)
+
+
+def close(out, ref, dtype, W):
+    err = (out.float().cpu() - ref).abs()
+    return bool((err <= ref.abs() * TOL[dtype] + 1e-6 * W).all())
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    W = int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    w = tccl.init()
+    failures, ran = [], []
+
+    def case(name, fn):
+        try:
+            ok = fn()
+            torch.cuda.synchronize()
+            w.check()
+            ran.append(name)
+            if ok is False:
+                failures.append(name)
+        except Exception as e:  # noqa: BLE001
+            failures.append(f"{name}: {type(e).__name__}: {e}")
+            traceback.print_exc()
+
+    nvls = w.has_nvls
+    ar_algos = ["oneshot_p2p", "twoshot_p2p"] + (["oneshot_nvls", "twoshot_nvls"] if nvls else [])
+
+    # barriers
+    case("barrier_p2p", lambda: tccl.barrier(blocks=8, threads=64, rounds=20))
+    if nvls:
+        case("barrier_nvls", lambda: tccl.barrier(blocks=8, threads=64, rounds=20, flavour="nvls"))
+
+    def cas():
+        t = w.empty(4096, torch.int32)
+        t.zero_()
+        h = w.handle(t)
+        for _ in range(3):
+            tccl.barrier_test(h, blocks=32, threads=128)
+        torch.cuda.synchronize()
+        pad = h.get_signal_pad(w.rank, (32 * W,), dtype=torch.int32)
+        return int(pad.abs().sum()) == 0
+    case("barrier_cas_on_torch_pads", cas)
+
+    for dtype in (torch.bfloat16, torch.float32):
+        for n in (8, 4096 + 8, 100003, 1 << 20, (1 << 24) + 16):
+            xs = [seeded(n, dtype, 2000 + r) for r in range(W)]
+            ref = torch.stack([x.float() for x in xs]).sum(0)
+            x = w.empty(n, dtype)
+            for algo in ar_algos:
+                def ar(algo=algo):
+                    x.copy_(xs[rank])
+                    if algo.startswith("oneshot"):
+                        out = tccl.all_reduce(x, algo=algo)
+                        return close(out, ref, dtype, W) and torch.equal(x.cpu(), xs[rank])
+                    tccl.all_reduce(x, inplace=True, algo=algo)
+                    return close(x, ref, dtype, W)
+                case(f"allreduce/{algo}/{dtype}/{n}", ar)
+            if n % (W * 8) == 0:
+                for algo in ["p2p"] + (["nvls"] if nvls else []):
+                    def rs(algo=algo):
+                        x.copy_(xs[rank])
+                        out = tccl.reduce_scatter(x, algo=algo)
+                        per = n // W
+                        return close(out, ref[rank * per:(rank + 1) * per], dtype, W)
+                    case(f"reducescatter/{algo}/{dtype}/{n}", rs)
+
+    for n in (8, 1003, 1 << 16, (1 << 22) + 8):
+        xs = [seeded(n, torch.bfloat16, 3000 + r, "uniform") for r in range(W)]
+        ref = torch.stack(xs)
+        x = w.empty(n, torch.bfloat16)
+        x.copy_(xs[rank])
+
+        def pull():
+            return torch.equal(tccl.one_shot_all_gather(x, W).cpu(), ref)
+        case(f"allgather/pull/{n}", pull)
+        if n % 8 == 0:
+            out = w.empty((W, n), torch.bfloat16)
+            for algo in ["push"] + (["push_nvls"] if nvls else []):
+                def push(algo=algo):
+                    out.zero_()
+                    tccl.all_gather(x, out=out, algo=algo)
+                    return torch.equal(out.cpu(), ref)
+                case(f"allgather/{algo}/{n}", push)
+
+    # back-to-back stress with changing data (WAR/RAW hazards)
+    def stress():
+        n = 4096
+        x = w.empty(n, torch.float32)
+        ok = True
+        for it in range(300):
+            x.fill_(float(it * (rank + 1)))
+            algo = ar_algos[it % len(ar_algos)]
+            if algo.startswith("oneshot"):
+                o = tccl.all_reduce(x, algo=algo)
+            else:
+                o = tccl.all_reduce(x, inplace=True, algo=algo)
+            if it % 50 == 49:
+                ok = ok and bool((o == float(it * W * (W + 1) // 2)).all())
+        return ok
+    case("stress", stress)
+
+    bad = torch.tensor([len(failures)], device="cuda")
+    dist.all_reduce(bad)
+    if rank == 0:
+        print(json.dumps({"world": W, "nvls": nvls, "cases": len(ran), "failures_rank0": failures,
+                          "total_failures": int(bad.item())}), flush=True)
+    elif failures:
+        print(f"[rank {rank}] failures: {failures}", flush=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(1 if int(bad.item()) else 0)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,249 @@
+"""Flat collectives and barriers with all ranks emulated on one GPU, against a
+plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.bfloat16, torch.float32, torch.float16]
+TOL = {torch.bfloat16: 2 ** -8, torch.float16: 2 ** -11, torch.float32: 1e-6}
+
+
+def make_inputs(world, W, n, dtype, seed):
+    parts = []
+    for r in range(W):
+        g = torch.Generator(device="cpu").manual_seed(seed + r)
+        parts.append(torch.randn(n, generator=g, dtype=torch.float32).to(dtype))
+    return world.from_parts(parts)
+
+
+def ref_sum(x):
+    return torch.stack([p.float() for p in x.parts]).sum(0)
+
+
+def assert_close_to_sum(out, ref, dtype, W):
+    # one rounding of an fp32 sum: half an ulp of the result, relative
+    err = (out.float() - ref).abs()
+    bound = ref.abs() * TOL[dtype] + 1e-6 * W
+    assert bool((err <= bound).all()), f"max err {err.max().item()} (bound {bound.max().item()})"
+
+
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("rounds,blocks", [(1, 1), (3, 7), (50, 16)])
+def test_barrier_p2p(emu_worlds, W, rounds, blocks):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    tccl.barrier(world=w, blocks=blocks, threads=64, rounds=rounds)
+    tccl.barrier(world=w, blocks=blocks, threads=64, rounds=rounds)
+    torch.cuda.synchronize()
+    w.check()
+    from tccl_b200.utils.lib import K
+    for r in range(W):
+        ep = w.local_states[r][K["TCCL_LOCAL_EPOCH"] : K["TCCL_LOCAL_EPOCH"] + blocks]
+        assert bool((ep == ep[0]).all())
+
+
+@pytest.mark.parametrize("W", [1, 2, 4, 8])
+def test_barrier_cas_on_pads_resets_to_zero(emu_worlds, W):
+    import tccl_b200 as tccl
+    from tccl_b200.parallel.emu import EmuTensor
+
+    w = emu_worlds(W)
+    pads = EmuTensor([torch.zeros(32 * W, dtype=torch.int32, device=w.device) for _ in range(W)])
+    for _ in range(5):
+        tccl.barrier_test(world=w, pads=pads, blocks=16 if W == 8 else 32, threads=128)
+    torch.cuda.synchronize()
+    w.check()
+    for p in pads:
+        assert int(p.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n", [8, 4096 + 8, 100003, 1 << 20])
+def test_all_reduce_oneshot(emu_worlds, W, dtype, n):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    x = make_inputs(w, W, n, dtype, 1000)
+    keep = [p.clone() for p in x.parts]
+    out = tccl.all_reduce(x, algo="oneshot_p2p", world=w)
+    torch.cuda.synchronize()
+    w.check()
+    ref = ref_sum(x)
+    for r in range(W):
+        assert_close_to_sum(out[r], ref, dtype, W)
+        assert torch.equal(out[r], out[0])
+        assert torch.equal(x[r], keep[r])
+
+
+def test_all_reduce_fill_rank_exact(emu_worlds):
+    """The reference's own check: fill with the rank, expect W (W-1) / 2
+    (triton_one_shot_all_reduce_no_128.py:116-127)."""
+    import tccl_b200 as tccl
+
+    W = 8
+    w = emu_worlds(W)
+    x = w.from_parts([torch.full((8192,), float(r), dtype=torch.bfloat16) for r in range(W)])
+    out = tccl.one_shot_all_reduce(x, world=w)
+    torch.cuda.synchronize()
+    for r in range(W):
+        assert bool(out[r].eq(W * (W - 1) // 2).all())
+
+
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [8, 1000, 65536 + 24, 3 * (1 << 20) + 5])
+def test_all_reduce_twoshot_inplace(emu_worlds, W, dtype, n):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    x = make_inputs(w, W, n, dtype, 2000)
+    ref = ref_sum(x)
+    res = tccl.all_reduce(x, inplace=True, algo="twoshot_p2p", world=w)
+    torch.cuda.synchronize()
+    w.check()
+    assert res is x
+    for r in range(W):
+        assert_close_to_sum(x[r], ref, dtype, W)
+        assert torch.equal(x[r], x[0])
+
+
+def test_all_reduce_twoshot_symmetric_out_keeps_input(emu_worlds):
+    import tccl_b200 as tccl
+
+    W, n = 4, 50000
+    w = emu_worlds(W)
+    x = make_inputs(w, W, n, torch.bfloat16, 7)
+    keep = [p.clone() for p in x.parts]
+    out = w.empty(n, torch.bfloat16)
+    tccl.all_reduce(x, out=out, algo="twoshot_p2p", world=w)
+    torch.cuda.synchronize()
+    ref = ref_sum(x)
+    for r in range(W):
+        assert torch.equal(x[r], keep[r])
+        assert_close_to_sum(out[r], ref, torch.bfloat16, W)
+
+
+def test_auto_choice_and_views(emu_worlds):
+    """Views with a storage offset (tensor[:size], as every reference bench uses)."""
+    import tccl_b200 as tccl
+
+    W = 4
+    w = emu_worlds(W)
+    big = make_inputs(w, W, 1 << 16, torch.bfloat16, 11)
+    for lo, hi in [(0, 4096), (8, 8 + 1024), (1 << 15, 1 << 16)]:
+        v = big[lo:hi]
+        out = tccl.all_reduce(v, world=w)
+        torch.cuda.synchronize()
+        ref = ref_sum(v)
+        for r in range(W):
+            assert_close_to_sum(out[r], ref, torch.bfloat16, W)
+    with pytest.raises(ValueError):
+        tccl.all_reduce(big[3:11], world=w)  # 6-byte offset: not 16-byte aligned
+
+
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n", [8, 1003, 1 << 18])
+def test_all_gather_pull(emu_worlds, W, dtype, n):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    parts = []
+    for r in range(W):
+        g = torch.Generator(device="cpu").manual_seed(3000 + r)
+        parts.append((torch.rand(n, generator=g) * 2 - 1).to(dtype))
+    x = w.from_parts(parts)
+    out = tccl.one_shot_all_gather(x, W, world=w)
+    torch.cuda.synchronize()
+    w.check()
+    ref = torch.stack(list(x.parts))
+    for r in range(W):
+        assert out[r].shape == (W, n)
+        assert torch.equal(out[r], ref)
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+@pytest.mark.parametrize("n", [8, 1 << 12, (1 << 16) + 8])
+def test_all_gather_push(emu_worlds, W, n):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    x = make_inputs(w, W, n, torch.bfloat16, 3000)
+    out = w.empty((W, n), torch.bfloat16)
+    tccl.all_gather(x, out=out, algo="push", world=w)
+    torch.cuda.synchronize()
+    w.check()
+    ref = torch.stack(list(x.parts))
+    for r in range(W):
+        assert torch.equal(out[r], ref)
+
+
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("per_vec", [1, 37, 4096])
+def test_reduce_scatter(emu_worlds, W, dtype, per_vec):
+    import tccl_b200 as tccl
+
+    vpt = 16 // torch.empty(0, dtype=dtype).element_size()
+    n = per_vec * vpt * W
+    w = emu_worlds(W)
+    x = make_inputs(w, W, n, dtype, 3000)
+    out = tccl.one_shot_reduce_scatter(x, world=w)
+    torch.cuda.synchronize()
+    w.check()
+    ref = ref_sum(x).view(W, -1)
+    for r in range(W):
+        assert_close_to_sum(out[r], ref[r], dtype, W)
+    with pytest.raises(ValueError):
+        tccl.reduce_scatter(x[: n - vpt] if W > 1 else x[:1], world=w)
+
+
+def test_back_to_back_stress_changing_data(emu_worlds):
+    """1000 calls with the inputs rewritten between calls: a missing exit barrier
+    (write-after-read) or entry barrier (read-before-write) shows up as a wrong sum."""
+    import tccl_b200 as tccl
+
+    W, n = 4, 2048
+    w = emu_worlds(W)
+    x = w.empty(n, torch.float32)
+    for it in range(1000):
+        for r in range(W):
+            x[r].fill_(float(it * (r + 1)))
+        o = tccl.all_reduce(x, algo="oneshot_p2p", world=w)
+        if it % 100 == 99:
+            torch.cuda.synchronize()
+            expect = float(it * sum(range(1, W + 1)))
+            assert bool((o[0] == expect).all()) and bool((o[W - 1] == expect).all())
+    w.check()
+
+
+def test_timeout_is_reported_not_hung(emu_worlds):
+    """A wait that nothing satisfies returns after the limit with a TIMEOUT
+    status; the context stays usable and reset() clears the state."""
+    import time
+
+    import tccl_b200 as tccl
+    from tccl_b200.utils.lib import TcclTimeout
+
+    w = emu_worlds(2)
+    w.set_timeout_ms(200.0)
+    try:
+        t0 = time.time()
+        tccl.wait_never(world=w)
+        torch.cuda.synchronize()
+        assert time.time() - t0 < 5.0
+        st = w.last_status(0)
+        assert st["code"] == 1 and st["where"] == "TCCL_W_SIGNAL" and st["aborted"]
+        with pytest.raises(TcclTimeout):
+            w.check()
+    finally:
+        w.reset()
+        w.set_timeout_ms(2000.0)
+    w.check()
+    x = make_inputs(w, 2, 1024, torch.bfloat16, 5)
+    out = tccl.all_reduce(x, world=w)
+    torch.cuda.synchronize()
+    assert_close_to_sum(out[0], ref_sum(x), torch.bfloat16, 2)
