@@ -316,6 +316,18 @@ struct AllGatherPullP2P {
     const uint64_t rem = a.numel - nvec * VPT;
     const uint64_t nthr = (uint64_t)nb * blockDim.x;
     const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
+    if ((a.numel * sizeof(T)) & 15) {
+      // shard size not a multiple of 16 bytes: the output slots of ranks >= 1 are
+      // not vector aligned, so copy element by element
+      for (int k = 0; k < world; ++k) {
+        const int p = (c.rank + k + bid) % world;
+        const volatile T* src = reinterpret_cast<const volatile T*>(a.in[p]);
+        T* dst = reinterpret_cast<T*>(a.out) + (uint64_t)p * a.numel;
+        for (uint64_t e = tid; e < a.numel; e += nthr) dst[e] = src[e];
+      }
+      sync.exit(c, a.flags, bid);
+      return;
+    }
     for (int k = 0; k < world; ++k) {
       int p = c.rank + k + bid;
       p %= world;

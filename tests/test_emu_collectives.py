@@ -33,15 +33,17 @@ def assert_close_to_sum(out, ref, dtype, W):
 def test_barrier_p2p(emu_worlds, W, rounds, blocks):
     import tccl_b200 as tccl
 
+    from tccl_b200.utils.lib import K
+
     w = emu_worlds(W)
+    epochs = lambda r: w.local_states[r][K["TCCL_LOCAL_EPOCH"] : K["TCCL_LOCAL_EPOCH"] + blocks].clone()
+    before = [epochs(r) for r in range(W)]
     tccl.barrier(world=w, blocks=blocks, threads=64, rounds=rounds)
     tccl.barrier(world=w, blocks=blocks, threads=64, rounds=rounds)
     torch.cuda.synchronize()
     w.check()
-    from tccl_b200.utils.lib import K
     for r in range(W):
-        ep = w.local_states[r][K["TCCL_LOCAL_EPOCH"] : K["TCCL_LOCAL_EPOCH"] + blocks]
-        assert bool((ep == ep[0]).all())
+        assert bool((epochs(r) - before[r] == 2 * rounds).all())
 
 
 @pytest.mark.parametrize("W", [1, 2, 4, 8])
