@@ -187,7 +187,7 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 // --------------------------------------------------------- status / bounded wait
 __device__ __forceinline__ uint32_t* status_of(const tccl_comm& c) { return c.local + TCCL_LOCAL_STATUS; }
 
-__device__ __noinline__ void record_failure(const tccl_comm& c, int code, int peer, int where,
+static __device__ __noinline__ void record_failure(const tccl_comm& c, int code, int peer, int where,
                                             uint32_t seen, uint32_t want) {
   uint32_t* st = status_of(c);
   if (atomicCAS(st + TCCL_ST_CODE, 0u, (uint32_t)code) == 0u) {

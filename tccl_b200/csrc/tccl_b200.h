@@ -139,6 +139,21 @@ int tccl_allgather_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl
 int tccl_reducescatter_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_reducescatter_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 
+/* ---- double-binary-tree all-reduce --------------------------------------- */
+typedef struct tccl_tree_args {
+  void* buf[TCCL_MAX_WORLD]; /* every rank's symmetric buffer; reduced in place */
+  void* out;                 /* optional local copy of the result, or NULL */
+  uint64_t numel;            /* a whole number of 16-byte vectors */
+  uint64_t chunk_vecs;       /* 16-byte vectors per chunk; chunk c uses tree c % 2 */
+  int32_t dtype;
+  int32_t ctas_per_role;     /* K; the grid is 4 K CTAs (up/down x tree 0/1), K <= TCCL_TREE_MAX_CTAS */
+  int32_t parent[2];         /* neighbours in tree 0 / 1, -1 = none */
+  int32_t left[2];
+  int32_t right[2];
+  int32_t child_slot[2];     /* 0 if this rank is its parent's left child, 1 if right */
+} tccl_tree_args;
+int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,10 +7,17 @@ Reference API kept (``one_shot_all_reduce``, ``one_shot_all_gather``,
 widened: bf16 / fp32 / fp16, fp32 accumulation, any element count (ragged
 tails), ``out=`` to avoid the per-call allocation, in-place two-shot, and a
 size-based choice of kernel.
+
+Every call resolves to a *plan*: the validated, fully bound kernel launch.
+Plans are cached per (tensor address, size, dtype, destination, algorithm), so
+a repeated call costs one dictionary lookup and one C call — the reference
+instead re-runs ``rendezvous`` and re-specialises its kernel per size on every
+call.
 """
 from __future__ import annotations
 
-from typing import Optional
+import ctypes as C
+from typing import Callable, Dict, Optional
 
 import torch
 
@@ -32,10 +39,48 @@ _AR_KERNELS = {
 }
 
 
+class Plan:
+    """A bound launch.  ``run(out)``: ``out`` None → use/allocate the planned output."""
+
+    __slots__ = ("go", "args", "world", "result", "alloc", "post")
+
+    def __init__(self, world, go, args, result=None, alloc=None, post=None):
+        self.world, self.go, self.args, self.result, self.alloc, self.post = world, go, args, result, alloc, post
+
+    def run(self):
+        if self.alloc is not None:  # fresh local output(s) per call
+            outs = {}
+            for r, a in self.args.items():
+                o = self.alloc(r)
+                a.out = o.data_ptr()
+                outs[r] = o
+            self.go()
+            return self.world.wrap(outs)
+        self.go()
+        if self.post is not None:
+            self.post()
+        return self.result
+
+
+def _key(tag, w, x, out, *rest):
+    x0 = w.local(x, w.local_ranks[0])
+    o0 = None if out is None else w.local(out, w.local_ranks[0])
+    return (tag, x0.data_ptr(), x0.numel(), x0.dtype, 0 if o0 is None else o0.data_ptr(), *rest)
+
+
+def _cached(w: WorldBase, key, build: Callable[[], Plan]):
+    plans = w.plans
+    if plans is None:
+        return build().run()
+    p = plans.get(key)
+    if p is None:
+        p = plans[key] = build()
+    return p.run()
+
+
 def _base_args(world: WorldBase, x, dt: int, flags: int) -> L.CollArgs:
     a = L.CollArgs()
-    ptrs = world.peer_ptrs(x)
-    for p, v in enumerate(ptrs):
+    for p, v in enumerate(world.peer_ptrs(x)):
         a.inp[p] = v
     a.mc_in = world.mc_ptr(x)
     a.numel = world.local(x, world.local_ranks[0]).numel()
@@ -46,106 +91,8 @@ def _base_args(world: WorldBase, x, dt: int, flags: int) -> L.CollArgs:
 
 def _copy_args(a: L.CollArgs) -> L.CollArgs:
     b = L.CollArgs()
-    import ctypes as C
     C.memmove(C.byref(b), C.byref(a), C.sizeof(a))
     return b
-
-
-def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -> str:
-    """Size-based choice.  One-shot moves (W-1) S into every GPU but needs one
-    barrier round trip less and no symmetric destination: best for small
-    messages.  Two-shot moves about 2 (W-1)/W S (P2P) or S (NVLS) and needs a
-    symmetric destination (the input itself when in place)."""
-    cfg = world.config
-    if cfg.force_variant:
-        return cfg.force_variant
-    nvls = world.has_nvls
-    if world.world_size == 1:
-        return "oneshot_p2p"
-    if not symmetric_dst or nbytes <= cfg.oneshot_max_bytes:
-        return "oneshot_nvls" if nvls and nbytes <= 4 * cfg.oneshot_max_bytes else "oneshot_p2p"
-    return "twoshot_nvls" if nvls else "twoshot_p2p"
-
-
-def all_reduce(x, out=None, *, inplace: bool = False, algo: str = "auto", world: Optional[WorldBase] = None,
-               sync_exit: bool = True):
-    """Sum ``x`` over all ranks.
-
-    ``x`` lives in symmetric memory.  Result placement:
-
-    * ``inplace=True`` — the sum replaces ``x`` on every rank (two-shot or tree).
-    * ``out`` in symmetric memory — written by the two-shot kernels; ``x`` is kept.
-    * ``out`` an ordinary tensor or ``None`` — one-shot kernels; ``x`` is kept.
-
-    ``sync_exit=False`` drops the trailing barrier: the caller then promises not
-    to overwrite ``x`` before every rank has finished the call.
-    """
-    w = get_world(world)
-    check_sym_tensor(w, x, "all_reduce input")
-    x0 = w.local(x, w.local_ranks[0])
-    dt = dtype_code(x0.dtype)
-    nbytes = x0.numel() * x0.element_size()
-    if algo == "tree":
-        from .tree_allreduce import double_tree_all_reduce
-
-        return double_tree_all_reduce(x, out=out, inplace=inplace, world=w)
-    out_is_sym = out is not None and _is_symmetric(w, out)
-    sym_dst = inplace or out_is_sym
-    if algo == "auto":
-        algo = choose_all_reduce_algo(w, nbytes, sym_dst)
-    if algo not in _AR_KERNELS:
-        raise ValueError(f"unknown all-reduce algo {algo!r}")
-    if algo.endswith("nvls") and not w.has_nvls:
-        raise RuntimeError(f"{algo} needs NVLS multicast, which this world does not have")
-    flags = w.coll_flags(sync_exit=sync_exit)
-    base = _base_args(w, x, dt, flags)
-    vpt = 16 // x0.element_size()
-    nvec = x0.numel() // vpt
-    block = w.config.block
-    per_rank = {}
-    if algo.startswith("oneshot"):
-        if inplace:
-            # a one-shot result cannot land in the buffer peers are still reading: stage it
-            tmp = {r: torch.empty_like(w.local(x, r)) for r in w.local_ranks}
-            res = _launch_oneshot(w, algo, base, tmp, nvec, block, dt)
-            for r in w.local_ranks:
-                w.local(x, r).copy_(res[r])
-            return x
-        outs = {}
-        for r in w.local_ranks:
-            o = w.local(out, r) if out is not None else torch.empty_like(w.local(x, r))
-            _check_out(o, w.local(x, r))
-            outs[r] = o
-        _launch_oneshot(w, algo, base, outs, nvec, block, dt)
-        return out if out is not None else w.wrap(outs)
-    # two-shot: destination must be symmetric
-    if not sym_dst:
-        raise ValueError("two-shot all-reduce writes into symmetric memory: pass inplace=True or a symmetric out")
-    dst = x if inplace else out
-    check_sym_tensor(w, dst, "all_reduce destination")
-    dptrs = w.peer_ptrs(dst)
-    args = {}
-    for r in w.local_ranks:
-        a = _copy_args(base)
-        for p, v in enumerate(dptrs):
-            a.out_peer[p] = v
-        a.mc_out = w.mc_ptr(dst)
-        args[r] = a
-    per_slice = -(-nvec // w.world_size)
-    grid = grid_for(w, per_slice, block, 4)
-    w.launch(_AR_KERNELS[algo], args, grid, block, dt)
-    return dst
-
-
-def _launch_oneshot(w, algo, base, outs, nvec, block, dt):
-    args = {}
-    for r, o in outs.items():
-        a = _copy_args(base)
-        a.out = o.data_ptr()
-        args[r] = a
-    grid = grid_for(w, nvec, block, 4)
-    w.launch(_AR_KERNELS[algo], args, grid, block, dt)
-    return outs
 
 
 def _check_out(o: torch.Tensor, like: torch.Tensor, numel: Optional[int] = None) -> None:
@@ -166,6 +113,104 @@ def _is_symmetric(w: WorldBase, t) -> bool:
         return False
 
 
+def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -> str:
+    """Size-based choice.  One-shot moves (W-1) S into every GPU but needs no
+    symmetric destination and touches each byte once: best for small messages.
+    Two-shot moves about 2 (W-1)/W S (P2P) or (1 + 1/W) S (NVLS) and needs a
+    symmetric destination (the input itself when in place)."""
+    cfg = world.config
+    if cfg.force_variant:
+        return cfg.force_variant
+    nvls = world.has_nvls
+    if world.world_size == 1:
+        return "oneshot_p2p"
+    if not symmetric_dst or nbytes <= cfg.oneshot_max_bytes:
+        return "oneshot_nvls" if nvls and world.world_size > 2 and nbytes <= 4 * cfg.oneshot_max_bytes else "oneshot_p2p"
+    return "twoshot_nvls" if nvls and world.world_size > 2 else "twoshot_p2p"
+
+
+def all_reduce(x, out=None, *, inplace: bool = False, algo: str = "auto", world: Optional[WorldBase] = None,
+               sync_exit: bool = True):
+    """Sum ``x`` over all ranks.
+
+    ``x`` lives in symmetric memory.  Result placement:
+
+    * ``inplace=True`` — the sum replaces ``x`` on every rank (two-shot or tree).
+    * ``out`` in symmetric memory — written by the two-shot kernels; ``x`` is kept.
+    * ``out`` an ordinary tensor or ``None`` — one-shot kernels; ``x`` is kept.
+
+    ``sync_exit=False`` drops the trailing barrier: the caller then promises not
+    to overwrite ``x`` before every rank has finished the call.
+    """
+    w = get_world(world)
+    if algo == "tree":
+        from .tree_allreduce import double_tree_all_reduce
+
+        return double_tree_all_reduce(x, out=out, inplace=inplace, world=w)
+    return _cached(w, _key("ar", w, x, out, inplace, algo, sync_exit),
+                   lambda: _plan_all_reduce(w, x, out, inplace, algo, sync_exit))
+
+
+def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
+    check_sym_tensor(w, x, "all_reduce input")
+    x0 = w.local(x, w.local_ranks[0])
+    dt = dtype_code(x0.dtype)
+    nbytes = x0.numel() * x0.element_size()
+    out_is_sym = out is not None and _is_symmetric(w, out)
+    sym_dst = inplace or out_is_sym
+    if algo == "auto":
+        algo = choose_all_reduce_algo(w, nbytes, sym_dst)
+    if algo not in _AR_KERNELS:
+        raise ValueError(f"unknown all-reduce algo {algo!r}")
+    if algo.endswith("nvls") and not w.has_nvls:
+        raise RuntimeError(f"{algo} needs NVLS multicast, which this world does not have")
+    flags = w.coll_flags(sync_exit=sync_exit)
+    base = _base_args(w, x, dt, flags)
+    vpt = 16 // x0.element_size()
+    nvec = x0.numel() // vpt
+    block = w.config.block
+    if algo.startswith("oneshot"):
+        args = {r: _copy_args(base) for r in w.local_ranks}
+        grid = grid_for(w, nvec, block, 4)
+        go = w.prepare(_AR_KERNELS[algo], args, grid, block, dt)
+        if inplace:
+            # a one-shot result cannot land in the buffer peers are still reading: stage it
+            tmp = {r: torch.empty_like(w.local(x, r)) for r in w.local_ranks}
+            for r, a in args.items():
+                a.out = tmp[r].data_ptr()
+
+            def post():
+                for r in w.local_ranks:
+                    w.local(x, r).copy_(tmp[r])
+
+            return Plan(w, go, args, result=x, post=post)
+        if out is not None:
+            for r, a in args.items():
+                o = w.local(out, r)
+                _check_out(o, w.local(x, r))
+                a.out = o.data_ptr()
+            return Plan(w, go, args, result=out)
+        return Plan(w, go, args, alloc=lambda r: torch.empty_like(w.local(x, r)))
+    # two-shot: destination must be symmetric
+    if not sym_dst:
+        raise ValueError("two-shot all-reduce writes into symmetric memory: pass inplace=True or a symmetric out")
+    dst = x if inplace else out
+    check_sym_tensor(w, dst, "all_reduce destination")
+    if w.local(dst, w.local_ranks[0]).numel() != x0.numel() or w.local(dst, w.local_ranks[0]).dtype != x0.dtype:
+        raise ValueError("all_reduce destination must match the input's size and dtype")
+    dptrs = w.peer_ptrs(dst)
+    args = {}
+    for r in w.local_ranks:
+        a = _copy_args(base)
+        for p, v in enumerate(dptrs):
+            a.out_peer[p] = v
+        a.mc_out = w.mc_ptr(dst)
+        args[r] = a
+    per_slice = -(-nvec // w.world_size)
+    grid = grid_for(w, per_slice, block, 4)
+    return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt), args, result=dst)
+
+
 def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = None, sync_exit: bool = True):
     """Gather every rank's ``x`` into a ``(W, *x.shape)`` tensor on every rank.
 
@@ -176,6 +221,10 @@ def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = 
     trips), pull otherwise.
     """
     w = get_world(world)
+    return _cached(w, _key("ag", w, x, out, algo, sync_exit), lambda: _plan_all_gather(w, x, out, algo, sync_exit))
+
+
+def _plan_all_gather(w, x, out, algo, sync_exit) -> Plan:
     check_sym_tensor(w, x, "all_gather input")
     x0 = w.local(x, w.local_ranks[0])
     dt = dtype_code(x0.dtype)
@@ -183,7 +232,7 @@ def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = 
     nbytes = x0.numel() * x0.element_size()
     out_is_sym = out is not None and _is_symmetric(w, out)
     if algo == "auto":
-        if out_is_sym and nbytes <= (1 << 20):
+        if out_is_sym and nbytes <= (1 << 20) and nbytes % 16 == 0:
             algo = "push_nvls" if w.has_nvls else "push"
         else:
             algo = "pull"
@@ -193,16 +242,16 @@ def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = 
     nvec = x0.numel() // vpt
     block = w.config.block
     if algo == "pull":
-        outs, args = {}, {}
-        for r in w.local_ranks:
-            xr = w.local(x, r)
-            o = w.local(out, r) if out is not None else torch.empty((W, *xr.shape), dtype=xr.dtype, device=xr.device)
-            _check_out(o, xr, xr.numel() * W)
-            a = _copy_args(base)
-            a.out = o.data_ptr()
-            outs[r], args[r] = o, a
-        w.launch("tccl_allgather_pull_p2p", args, grid_for(w, nvec, block, 4), block, dt)
-        return out if out is not None else w.wrap(outs)
+        args = {r: _copy_args(base) for r in w.local_ranks}
+        go = w.prepare("tccl_allgather_pull_p2p", args, grid_for(w, nvec, block, 4), block, dt)
+        if out is not None:
+            for r, a in args.items():
+                o = w.local(out, r)
+                _check_out(o, w.local(x, r), x0.numel() * W)
+                a.out = o.data_ptr()
+            return Plan(w, go, args, result=out)
+        shape = (W, *x0.shape)
+        return Plan(w, go, args, alloc=lambda r: torch.empty(shape, dtype=x0.dtype, device=x0.device))
     if algo not in ("push", "push_nvls"):
         raise ValueError(f"unknown all-gather algo {algo!r}")
     if not out_is_sym:
@@ -210,8 +259,10 @@ def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = 
     if algo == "push_nvls" and not w.has_nvls:
         raise RuntimeError("push_nvls needs NVLS multicast")
     check_sym_tensor(w, out, "all_gather output")
-    if x0.numel() * x0.element_size() % 16:
+    if nbytes % 16:
         raise ValueError("push all-gather needs a shard size that is a multiple of 16 bytes")
+    if w.local(out, w.local_ranks[0]).numel() != x0.numel() * W:
+        raise ValueError("all_gather output must hold world_size shards")
     optrs = w.peer_ptrs(out)
     args = {}
     for r in w.local_ranks:
@@ -221,8 +272,7 @@ def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = 
         a.mc_out = w.mc_ptr(out)
         args[r] = a
     name = "tccl_allgather_push_nvls" if algo == "push_nvls" else "tccl_allgather_push_p2p"
-    w.launch(name, args, grid_for(w, nvec, block, 4), block, dt)
-    return out
+    return Plan(w, w.prepare(name, args, grid_for(w, nvec, block, 4), block, dt), args, result=out)
 
 
 def reduce_scatter(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = None, sync_exit: bool = True):
@@ -231,6 +281,10 @@ def reduce_scatter(x, out=None, *, algo: str = "auto", world: Optional[WorldBase
     As in the reference the element count must be a multiple of ``W`` times the
     16-byte vector width (``triton_reduce_scatter.py:102-104``)."""
     w = get_world(world)
+    return _cached(w, _key("rs", w, x, out, algo, sync_exit), lambda: _plan_reduce_scatter(w, x, out, algo, sync_exit))
+
+
+def _plan_reduce_scatter(w, x, out, algo, sync_exit) -> Plan:
     check_sym_tensor(w, x, "reduce_scatter input")
     x0 = w.local(x, w.local_ranks[0])
     dt = dtype_code(x0.dtype)
@@ -240,25 +294,24 @@ def reduce_scatter(x, out=None, *, algo: str = "auto", world: Optional[WorldBase
         raise ValueError(f"numel must be a multiple of {vpt * W} (vector width x world size)")
     per = x0.numel() // W
     if algo == "auto":
-        algo = w.config.force_variant or ("nvls" if w.has_nvls else "p2p")
+        algo = w.config.force_variant or ("nvls" if w.has_nvls and W > 2 else "p2p")
     if algo not in ("p2p", "nvls"):
         raise ValueError(f"unknown reduce-scatter algo {algo!r}")
     if algo == "nvls" and not w.has_nvls:
         raise RuntimeError("nvls reduce-scatter needs NVLS multicast")
     flags = w.coll_flags(sync_exit=sync_exit)
     base = _base_args(w, x, dt, flags)
-    outs, args = {}, {}
-    for r in w.local_ranks:
-        xr = w.local(x, r)
-        o = w.local(out, r) if out is not None else torch.empty(per, dtype=xr.dtype, device=xr.device)
-        _check_out(o, xr, per)
-        a = _copy_args(base)
-        a.out = o.data_ptr()
-        outs[r], args[r] = o, a
+    args = {r: _copy_args(base) for r in w.local_ranks}
     block = w.config.block
     name = "tccl_reducescatter_nvls" if algo == "nvls" else "tccl_reducescatter_p2p"
-    w.launch(name, args, grid_for(w, per // vpt, block, 4), block, dt)
-    return out if out is not None else w.wrap(outs)
+    go = w.prepare(name, args, grid_for(w, per // vpt, block, 4), block, dt)
+    if out is not None:
+        for r, a in args.items():
+            o = w.local(out, r)
+            _check_out(o, w.local(x, r), per)
+            a.out = o.data_ptr()
+        return Plan(w, go, args, result=out)
+    return Plan(w, go, args, alloc=lambda r: torch.empty(per, dtype=x0.dtype, device=x0.device))
 
 
 # ---- reference-named entry points -------------------------------------------
@@ -266,7 +319,7 @@ def one_shot_all_reduce(tensor, out=None, world: Optional[WorldBase] = None):
     """``out = sum over ranks of tensor``; returns a new ordinary tensor."""
     w = get_world(world)
     algo = w.config.force_variant if w.config.force_variant.startswith("oneshot") else (
-        "oneshot_nvls" if w.has_nvls and w.world_size > 1 else "oneshot_p2p")
+        "oneshot_nvls" if w.has_nvls and w.world_size > 2 else "oneshot_p2p")
     return all_reduce(tensor, out=out, algo=algo, world=w)
 
 

@@ -72,6 +72,7 @@ class EmuWorld(WorldBase):
         self.stages = [torch.empty(self._stage_bytes, dtype=torch.uint8, device=self.device) for _ in range(W)]
         self.local_states = [torch.zeros(K["TCCL_LOCAL_WORDS"], dtype=torch.int32, device=self.device) for _ in range(W)]
         self._keep = []
+        self.plans = None  # emulated launches are not cached
         self._upload_comms()
 
     def _upload_comms(self):
@@ -139,21 +140,30 @@ class EmuWorld(WorldBase):
     def max_ctas(self) -> int:
         return min(super().max_ctas(), self.resident_cta_limit(self.config.block))
 
-    def launch(self, name, args_by_rank, grid, block, dtype_code=0, stream=None):
+    def prepare(self, name, args_by_rank, grid, block, dtype_code=0):
         W = self.world_size
         first = args_by_rank[0]
-        arr = (type(first) * W)()
-        for r in range(W):
-            C.memmove(C.byref(arr[r]), C.byref(args_by_rank[r]), C.sizeof(first))
-        args_dev = self._to_device(arr)
-        self._keep.append(args_dev)
-        if len(self._keep) > 64:
-            torch.cuda.synchronize(self.device)
-            del self._keep[:-1]
-        s = stream or torch.cuda.current_stream(self.device)
-        l = L.Launch(int(grid), int(block), W, int(dtype_code), C.c_void_p(s.cuda_stream))
-        L.call(name, C.c_void_p(self.comms_dev.data_ptr()), C.c_void_p(args_dev.data_ptr()), l)
-        self.launches += 1
+        fn = getattr(L.lib(), name)
+        l = L.Launch(int(grid), int(block), W, int(dtype_code), None)
+        comms = C.c_void_p(self.comms_dev.data_ptr())
+
+        def go():
+            # the structs may have been patched since the last call: upload them again
+            arr = (type(first) * W)()
+            for r in range(W):
+                C.memmove(C.byref(arr[r]), C.byref(args_by_rank[r]), C.sizeof(first))
+            args_dev = self._to_device(arr)
+            self._keep.append(args_dev)
+            if len(self._keep) > 64:
+                torch.cuda.synchronize(self.device)
+                del self._keep[:-1]
+            l.stream = torch.cuda.current_stream(self.device).cuda_stream
+            rc = fn(comms, C.c_void_p(args_dev.data_ptr()), C.byref(l))
+            if rc:
+                L.check(rc, name)
+            self.launches += 1
+
+        return go
 
     # -- state
     def last_status(self, rank: int = None):

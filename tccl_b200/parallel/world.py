@@ -76,9 +76,16 @@ class WorldBase:
         """Turn {rank: tensor} into what this world hands back to the user."""
         raise NotImplementedError
 
-    def launch(self, name: str, args_by_rank: Dict[int, C.Structure], grid: int, block: int,
-               dtype_code: int = 0, stream: Optional[torch.cuda.Stream] = None) -> None:
+    def prepare(self, name: str, args_by_rank: Dict[int, C.Structure], grid: int, block: int,
+                dtype_code: int = 0):
+        """Bind one kernel launch to its arguments; returns a zero-argument callable
+        that enqueues it on the current stream.  The argument structs stay owned by
+        the caller, who may patch a field (an output pointer) between calls."""
         raise NotImplementedError
+
+    def launch(self, name: str, args_by_rank: Dict[int, C.Structure], grid: int, block: int,
+               dtype_code: int = 0) -> None:
+        self.prepare(name, args_by_rank, grid, block, dtype_code)()
 
     def empty(self, shape, dtype=torch.bfloat16):
         raise NotImplementedError
@@ -129,6 +136,7 @@ class RealWorld(WorldBase):
         except Exception:
             pass
         self._handles: Dict[int, tuple] = {}
+        self.plans: Dict[tuple, object] = {}  # op wrappers cache their bound launches here
         # workspace = [flag region | staging area], one symmetric allocation
         self._flag_bytes = -(-K["TCCL_FLAG_WORDS"] * 4 // 65536) * 65536
         self._stage_bytes = int(self.config.stage_mb) << 20
@@ -170,11 +178,18 @@ class RealWorld(WorldBase):
             hdl = self._symm.rendezvous(t, self.group)
             base = [int(p) for p in hdl.buffer_ptrs]
             mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
-            ent = (hdl, base, mc, base[self.rank])
+            # the entry keeps `t` alive: a symmetric allocation stays mapped (and its
+            # address cannot be reused by another allocation) until free() drops it
+            ent = (hdl, base, mc, base[self.rank], t)
             self._handles[key] = ent
-        hdl, base, mc, local_base = ent
+        hdl, base, mc, local_base = ent[:4]
         delta = t.data_ptr() - local_base
         return [b + delta for b in base], (mc + delta if mc else 0)
+
+    def free(self, t: torch.Tensor) -> None:
+        """Forget a symmetric allocation (and every cached launch that points into it)."""
+        self._handles.pop(t.untyped_storage().data_ptr(), None)
+        self.plans.clear()
 
     def handle(self, t: torch.Tensor):
         """The torch symmetric-memory handle of ``t``'s allocation."""
@@ -215,11 +230,23 @@ class RealWorld(WorldBase):
         raw = self.workspace[self._flag_bytes + offset : self._flag_bytes + offset + nbytes]
         return raw.view(dtype)
 
-    def launch(self, name, args_by_rank, grid, block, dtype_code=0, stream=None):
-        s = stream or torch.cuda.current_stream(self.device)
-        l = L.Launch(int(grid), int(block), 0, int(dtype_code), C.c_void_p(s.cuda_stream))
-        L.call(name, C.byref(self.comm), C.byref(args_by_rank[self.rank]), l)
-        self.launches += 1
+    def prepare(self, name, args_by_rank, grid, block, dtype_code=0):
+        fn = getattr(L.lib(), name)
+        a = args_by_rank[self.rank]
+        l = L.Launch(int(grid), int(block), 0, int(dtype_code), None)
+        comm_ref, a_ref, l_ref = C.byref(self.comm), C.byref(a), C.byref(l)
+        raw_stream = torch._C._cuda_getCurrentRawStream
+        dev = self.device.index
+
+        def go():
+            l.stream = raw_stream(dev)
+            rc = fn(comm_ref, a_ref, l_ref)
+            if rc:
+                L.check(rc, name)
+            self.launches += 1
+
+        go.keep = (a, l)  # the structs the references point into
+        return go
 
     # -- state
     def last_status(self) -> dict:

@@ -83,6 +83,21 @@ class PadsArgs(C.Structure):
     _fields_ = [("pads", C.c_uint64 * MAX_WORLD)]
 
 
+class TreeArgs(C.Structure):
+    _fields_ = [
+        ("buf", C.c_uint64 * MAX_WORLD),
+        ("out", C.c_uint64),
+        ("numel", C.c_uint64),
+        ("chunk_vecs", C.c_uint64),
+        ("dtype", C.c_int32),
+        ("ctas_per_role", C.c_int32),
+        ("parent", C.c_int32 * 2),
+        ("left", C.c_int32 * 2),
+        ("right", C.c_int32 * 2),
+        ("child_slot", C.c_int32 * 2),
+    ]
+
+
 class Launch(C.Structure):
     _fields_ = [
         ("grid", C.c_int32),

@@ -249,3 +249,42 @@ def test_timeout_is_reported_not_hung(emu_worlds):
     out = tccl.all_reduce(x, world=w)
     torch.cuda.synchronize()
     assert_close_to_sum(out[0], ref_sum(x), torch.bfloat16, 2)
+
+
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,chunk_kb", [(8, 512), (4096, 1), (100000, 4), ((1 << 20) + 64, 64), (3 << 20, 512)])
+def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    old = w.config.tree_chunk_bytes
+    w.config.tree_chunk_bytes = chunk_kb * 1024
+    try:
+        x = make_inputs(w, W, n, dtype, 2000)
+        keep = [p.clone() for p in x.parts]
+        ref = ref_sum(x)
+        out = tccl.double_tree_all_reduce(x, world=w)
+        torch.cuda.synchronize()
+        w.check()
+        for r in range(W):
+            # tree order != rank order: a few roundings of partial sums on the way up
+            err = (out[r].float() - ref).abs()
+            steps = max(1, W.bit_length())
+            assert bool((err <= ref.abs() * TOL[dtype] * steps + (2e-2 if dtype != torch.float32 else 1e-5) * steps).all())
+            assert torch.equal(out[r], out[0])
+            assert torch.equal(x[r], keep[r])
+        # in place, twice in a row (counters must be back at zero)
+        for _ in range(2):
+            y = w.from_parts([p.clone() for p in keep])
+            tccl.all_reduce(y, inplace=True, algo="tree", world=w)
+            torch.cuda.synchronize()
+            w.check()
+            for r in range(W):
+                assert torch.equal(y[r], out[0])
+    finally:
+        w.config.tree_chunk_bytes = old
+    from tccl_b200.utils.lib import K
+    for r in range(W):
+        lo, hi = K["TCCL_FLAG_TREE_UP"], K["TCCL_FLAG_TILE"]
+        assert int(w.flags[r][lo:hi].abs().sum()) == 0
