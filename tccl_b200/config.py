@@ -31,8 +31,8 @@ class Config:
     nvls_barrier: bool = False        # barrier flavour used inside data kernels
     force_variant: str = ""           # e.g. "oneshot_p2p"; empty = size-based choice
     oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
-    tree_chunk_bytes: int = 512 * 1024    # double-tree: bytes per chunk (per tree)
-    tree_ctas: int = 16                   # double-tree: CTAs per (tree, direction)
+    tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
+    tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
     debug: bool = False
 
     @classmethod

@@ -34,7 +34,8 @@ template <typename T>
 struct TreeAllReduce {
   using Args = tccl_tree_args;
   static constexpr int kMaxThreads = 512, kMinBlocks = 1;
-  static constexpr int U = 4;
+  static constexpr int U = 4;   // vectors in flight per thread and source, up phase
+  static constexpr int UD = 8;  // down phase (one source)
 
   static __device__ __forceinline__ uint32_t* up_flag(const tccl_comm& c, int rank, int tree, int k, int slot) {
     return c.flags[rank] + TCCL_FLAG_TREE_UP + ((tree * TCCL_TREE_MAX_CTAS + k) * 2 + slot);
@@ -140,12 +141,12 @@ struct TreeAllReduce {
         const uint64_t clo = (2 * n + tree) * cv, chi = min(clo + cv, nvec);
         const uint64_t per = (chi - clo + K - 1) / K, lo = min(clo + per * k, chi), hi = min(lo + per, chi);
         uint64_t i = lo + t;
-        for (; i + (U - 1) * (uint64_t)nt < hi; i += (uint64_t)U * nt) {
-          Vec16 v[U];
+        for (; i + (UD - 1) * (uint64_t)nt < hi; i += (uint64_t)UD * nt) {
+          Vec16 v[UD];
 #pragma unroll
-          for (int u = 0; u < U; ++u) v[u] = ld_peer(pbuf + (i + (uint64_t)u * nt) * 16);
+          for (int u = 0; u < UD; ++u) v[u] = ld_peer(pbuf + (i + (uint64_t)u * nt) * 16);
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < UD; ++u) {
             const uint64_t off = (i + (uint64_t)u * nt) * 16;
             st_peer(own + off, v[u]);
             if (out) st_local(out + off, v[u]);

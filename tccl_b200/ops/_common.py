@@ -48,6 +48,8 @@ def grid_for(world: WorldBase, nvec: int, block: int, per_thread: int, cap: Opti
     on every rank (it depends only on the size and the shared configuration)."""
     want = -(-max(nvec, 1) // (block * per_thread))
     m = world.max_ctas()
+    if world.world_size == 1:
+        m = world.local_copy_ctas()
     if cap:
         m = min(m, cap)
     return max(1, min(want, m))

@@ -32,9 +32,14 @@ def _tree_grid(w: WorldBase, nbytes: int):
     """(K, chunk_vecs): CTAs per role and 16-byte vectors per chunk."""
     cfg = w.config
     kmax = min(cfg.tree_ctas, K["TCCL_TREE_MAX_CTAS"], max(1, w.max_ctas() // 4))
-    # at least 32 KiB per CTA per chunk, or the per-chunk handshake dominates
-    k = max(1, min(kmax, nbytes // (2 * 32768)))
-    chunk_bytes = max(cfg.tree_chunk_bytes, k * 32768)
+    # at least 64 KiB per CTA per chunk, or the per-chunk handshake dominates
+    k = max(1, min(kmax, nbytes // (2 * 65536)))
+    if cfg.tree_chunk_bytes < 65536:
+        chunk_bytes = cfg.tree_chunk_bytes  # small chunks on request (tests of the pipeline)
+    else:
+        floor = k * 65536
+        # keep several chunks per tree in flight even for medium messages
+        chunk_bytes = max(floor, min(cfg.tree_chunk_bytes, nbytes // 8))
     chunk_vecs = max(1, chunk_bytes // 16)
     return k, chunk_vecs
 

@@ -140,6 +140,9 @@ class EmuWorld(WorldBase):
     def max_ctas(self) -> int:
         return min(super().max_ctas(), self.resident_cta_limit(self.config.block))
 
+    def local_copy_ctas(self) -> int:
+        return self.max_ctas()  # cooperative launch: stay within what is co-resident
+
     def prepare(self, name, args_by_rank, grid, block, dtype_code=0):
         W = self.world_size
         first = args_by_rank[0]

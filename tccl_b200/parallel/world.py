@@ -100,6 +100,10 @@ class WorldBase:
         m = self.config.max_ctas or self.num_sms()
         return max(1, min(m, K["TCCL_MAX_BLOCKS"]))
 
+    def local_copy_ctas(self) -> int:
+        """A one-rank collective is a local copy: HBM-bound, wants several CTAs per SM."""
+        return min(4 * self.max_ctas(), K["TCCL_MAX_BLOCKS"])
+
     def coll_flags(self, sync_entry: bool = True, sync_exit: bool = True) -> int:
         f = 0
         if not sync_entry:
@@ -271,3 +275,13 @@ class RealWorld(WorldBase):
     def set_timeout_ms(self, ms: float) -> None:
         self.config.timeout_ms = ms
         self.comm.timeout_ns = self.config.timeout_ns
+
+    def reconfigure(self, **kw) -> None:
+        """Change configuration fields (identically on every rank) and drop the
+        cached launches that were sized with the old values."""
+        for k, v in kw.items():
+            if not hasattr(self.config, k):
+                raise AttributeError(k)
+            setattr(self.config, k, v)
+        self.comm.timeout_ns = self.config.timeout_ns
+        self.plans.clear()
