@@ -112,6 +112,17 @@ struct Entry {
   }
 };
 
+// Loop shape shared by the data kernels: in one sweep the grid covers one
+// contiguous window of nb * blockDim.x * U vectors (CTA b owns the b-th
+// blockDim.x * U slab of it, thread t the vectors t, t + blockDim.x, ... of the
+// slab), then the window advances.  All CTAs of all GPUs therefore stream
+// through the same few megabytes at a time, which keeps DRAM pages and TLB
+// entries hot on the GPUs being read; a plain grid-stride loop scatters each
+// thread's U accesses megabytes apart.
+#define TCCL_FOR_SLABS(U, n, bid, nb, i0)                                           \
+  for (uint64_t i0 = (uint64_t)(bid) * blockDim.x * (U) + threadIdx.x; i0 < (n);    \
+       i0 += (uint64_t)(nb) * blockDim.x * (U))
+
 // ---------------------------------------------------- one-shot all-reduce, P2P
 // out[i] = sum_r in_r[i]; every rank pulls all W copies (W-1 over NVLink).
 template <typename T, int W>
@@ -125,36 +136,29 @@ struct AllReduceOneShotP2P {
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
     const uint64_t nvec = a.numel / VPT;
-    const uint64_t nthr = (uint64_t)nb * blockDim.x;
-    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
-    uint64_t i = tid;
-    for (; i + (U - 1) * nthr < nvec; i += U * nthr) {
+    const uint64_t bs = blockDim.x;
+    TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
       Vec16 v[kMaxW][U];
 #pragma unroll
       for (int p = 0; p < kMaxW; ++p)
         if (p < world) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) v[p][u] = ld_peer(vptr<T>(a.in[p], i + u * nthr));
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * bs < nvec) v[p][u] = ld_peer(vptr<T>(a.in[p], i0 + u * bs));
         }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        Acc<T> acc;
-        acc.zero();
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < nvec) {
+          Acc<T> acc;
+          acc.zero();
 #pragma unroll
-        for (int p = 0; p < kMaxW; ++p)
-          if (p < world) acc.add(v[p][u]);
-        st_local(vptr<T>(a.out, i + u * nthr), acc.pack());
-      }
-    }
-    for (; i < nvec; i += nthr) {
-      Acc<T> acc;
-      acc.zero();
-#pragma unroll
-      for (int p = 0; p < kMaxW; ++p)
-        if (p < world) acc.add(ld_peer(vptr<T>(a.in[p], i)));
-      st_local(vptr<T>(a.out, i), acc.pack());
+          for (int p = 0; p < kMaxW; ++p)
+            if (p < world) acc.add(v[p][u]);
+          st_local(vptr<T>(a.out, i0 + u * bs), acc.pack());
+        }
     }
     // ragged tail (numel not a multiple of the vector width)
+    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if (tid < a.numel - nvec * VPT) {
       const uint64_t e = nvec * VPT + tid;
       float s = 0.f;
@@ -177,17 +181,17 @@ struct AllReduceOneShotNvls {
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
     const uint64_t nvec = a.numel / VPT;
-    const uint64_t nthr = (uint64_t)nb * blockDim.x;
-    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
-    uint64_t i = tid;
-    for (; i + (U - 1) * nthr < nvec; i += U * nthr) {
+    const uint64_t bs = blockDim.x;
+    TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
       Vec16 v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i + u * nthr));
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < nvec) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i0 + u * bs));
 #pragma unroll
-      for (int u = 0; u < U; ++u) st_local(vptr<T>(a.out, i + u * nthr), v[u]);
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < nvec) st_local(vptr<T>(a.out, i0 + u * bs), v[u]);
     }
-    for (; i < nvec; i += nthr) st_local(vptr<T>(a.out, i), MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i)));
+    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if (tid < a.numel - nvec * VPT) {
       const uint64_t e = nvec * VPT + tid;
       float s = 0.f;
@@ -217,42 +221,32 @@ struct AllReduceTwoShotP2P {
     constexpr int VPT = VecOf<T>::n;
     const uint64_t nvec = a.numel / VPT;
     const uint64_t per = (nvec + world - 1) / world;
-    const uint64_t lo = min(per * (uint64_t)c.rank, nvec), hi = min(lo + per, nvec);
-    const uint64_t nthr = (uint64_t)nb * blockDim.x;
-    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
-    uint64_t i = lo + tid;
-    for (; i + (U - 1) * nthr < hi; i += U * nthr) {
+    const uint64_t lo = min(per * (uint64_t)c.rank, nvec), n = min(lo + per, nvec) - lo;
+    const uint64_t bs = blockDim.x;
+    TCCL_FOR_SLABS(U, n, bid, nb, i0) {
       Vec16 v[kMaxW][U];
 #pragma unroll
       for (int p = 0; p < kMaxW; ++p)
         if (p < world) {
 #pragma unroll
-          for (int u = 0; u < U; ++u) v[p][u] = ld_peer(vptr<T>(a.in[p], i + u * nthr));
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * bs < n) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i0 + u * bs));
         }
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        Acc<T> acc;
-        acc.zero();
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < n) {
+          Acc<T> acc;
+          acc.zero();
 #pragma unroll
-        for (int p = 0; p < kMaxW; ++p)
-          if (p < world) acc.add(v[p][u]);
-        const Vec16 r = acc.pack();
+          for (int p = 0; p < kMaxW; ++p)
+            if (p < world) acc.add(v[p][u]);
+          const Vec16 r = acc.pack();
 #pragma unroll
-        for (int p = 0; p < kMaxW; ++p)
-          if (p < world) st_peer(vptr<T>(a.out_peer[p], i + u * nthr), r);
-      }
+          for (int p = 0; p < kMaxW; ++p)
+            if (p < world) st_peer(vptr<T>(a.out_peer[p], lo + i0 + u * bs), r);
+        }
     }
-    for (; i < hi; i += nthr) {
-      Acc<T> acc;
-      acc.zero();
-#pragma unroll
-      for (int p = 0; p < kMaxW; ++p)
-        if (p < world) acc.add(ld_peer(vptr<T>(a.in[p], i)));
-      const Vec16 r = acc.pack();
-#pragma unroll
-      for (int p = 0; p < kMaxW; ++p)
-        if (p < world) st_peer(vptr<T>(a.out_peer[p], i), r);
-    }
+    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if (c.rank == 0 && tid < a.numel - nvec * VPT) {
       const uint64_t e = nvec * VPT + tid;
       float s = 0.f;
@@ -265,31 +259,31 @@ struct AllReduceTwoShotP2P {
 
 // --------------------------------------------------- two-shot all-reduce, NVLS
 // Rank r ld_reduces slice r through the switch and multimem.st's the sum to
-// slice r of every rank's destination.  Per GPU about S bytes in and S bytes
+// slice r of every rank's destination.  Per GPU about (1 + 1/W) S bytes in and
 // out instead of 2 (W-1)/W S in for the P2P form.
 template <typename T, int W>
 struct AllReduceTwoShotNvls {
   using Args = tccl_coll_args;
   static constexpr int kMaxThreads = 512, kMinBlocks = 1;
-  static constexpr int U = 4;
+  static constexpr int U = 8;
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
     Entry sync(c, a.flags, bid);
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
     const uint64_t nvec = a.numel / VPT;
     const uint64_t per = (nvec + world - 1) / world;
-    const uint64_t lo = min(per * (uint64_t)c.rank, nvec), hi = min(lo + per, nvec);
-    const uint64_t nthr = (uint64_t)nb * blockDim.x;
-    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
-    uint64_t i = lo + tid;
-    for (; i + (U - 1) * nthr < hi; i += U * nthr) {
+    const uint64_t lo = min(per * (uint64_t)c.rank, nvec), n = min(lo + per, nvec) - lo;
+    const uint64_t bs = blockDim.x;
+    TCCL_FOR_SLABS(U, n, bid, nb, i0) {
       Vec16 v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i + u * nthr));
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < n) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i0 + u * bs));
 #pragma unroll
-      for (int u = 0; u < U; ++u) multimem_st(vptr<T>(a.mc_out, i + u * nthr), v[u]);
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < n) multimem_st(vptr<T>(a.mc_out, lo + i0 + u * bs), v[u]);
     }
-    for (; i < hi; i += nthr) multimem_st(vptr<T>(a.mc_out, i), MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i)));
+    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if (c.rank == 0 && tid < a.numel - nvec * VPT) {
       const uint64_t e = nvec * VPT + tid;
       float s = 0.f;
@@ -307,13 +301,13 @@ template <typename T, int W>
 struct AllGatherPullP2P {
   using Args = tccl_coll_args;
   static constexpr int kMaxThreads = 512, kMinBlocks = 1;
-  static constexpr int U = 4;
+  static constexpr int U = 8;
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
     Entry sync(c, a.flags, bid);
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
     const uint64_t nvec = a.numel / VPT;
-    const uint64_t rem = a.numel - nvec * VPT;
+    const uint64_t bs = blockDim.x;
     const uint64_t nthr = (uint64_t)nb * blockDim.x;
     const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if ((a.numel * sizeof(T)) & 15) {
@@ -329,21 +323,18 @@ struct AllGatherPullP2P {
       return;
     }
     for (int k = 0; k < world; ++k) {
-      int p = c.rank + k + bid;
-      p %= world;
+      const int p = (c.rank + k + bid) % world;
       const void* src = a.in[p];
       char* dst = reinterpret_cast<char*>(a.out) + (uint64_t)p * a.numel * sizeof(T);
-      uint64_t i = tid;
-      for (; i + (U - 1) * nthr < nvec; i += U * nthr) {
+      TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
         Vec16 v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = ld_peer(vptr<T>(src, i + u * nthr));
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * bs < nvec) v[u] = ld_peer(vptr<T>(src, i0 + u * bs));
 #pragma unroll
-        for (int u = 0; u < U; ++u) st_local(dst + (i + u * nthr) * 16, v[u]);
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * bs < nvec) st_local(dst + (i0 + u * bs) * 16, v[u]);
       }
-      for (; i < nvec; i += nthr) st_local(dst + i * 16, ld_peer(vptr<T>(src, i)));
-      if (tid < rem)
-        reinterpret_cast<T*>(dst)[nvec * VPT + tid] = reinterpret_cast<const volatile T*>(src)[nvec * VPT + tid];
     }
     sync.exit(c, a.flags, bid);
   }
@@ -373,25 +364,18 @@ struct AllGatherPush {
     Entry sync(c, a.flags, bid);
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
-    const uint64_t nvec = a.numel / VPT;
-    const uint64_t rem = a.numel - nvec * VPT;
-    const uint64_t nthr = (uint64_t)nb * blockDim.x;
-    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
+    const uint64_t nvec = a.numel / VPT;  // the host guarantees a whole number of vectors
+    const uint64_t bs = blockDim.x;
     const void* src = a.in[c.rank];
     const uint64_t base = (uint64_t)c.rank * a.numel * sizeof(T);
-    uint64_t i = tid;
-    for (; i + (U - 1) * nthr < nvec; i += U * nthr) {
+    TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
       Vec16 v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = ld_peer(vptr<T>(src, i + u * nthr));
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < nvec) v[u] = ld_peer(vptr<T>(src, i0 + u * bs));
 #pragma unroll
-      for (int u = 0; u < U; ++u) put(c, a, world, base + (i + u * nthr) * 16, v[u]);
-    }
-    for (; i < nvec; i += nthr) put(c, a, world, base + i * 16, ld_peer(vptr<T>(src, i)));
-    if (tid < rem) {
-      const T x = reinterpret_cast<const volatile T*>(src)[nvec * VPT + tid];
-      for (int p = 0; p < world; ++p)
-        reinterpret_cast<volatile T*>(reinterpret_cast<char*>(a.out_peer[p]) + base)[nvec * VPT + tid] = x;
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < nvec) put(c, a, world, base + (i0 + u * bs) * 16, v[u]);
     }
     sync.exit(c, a.flags, bid);
   }
@@ -405,54 +389,46 @@ struct ReduceScatter {
   using Args = tccl_coll_args;
   static constexpr int kMaxThreads = 512, kMinBlocks = 1;
   static constexpr int kMaxW = W ? W : TCCL_MAX_WORLD;
-  static constexpr int U = kNvls ? 4 : ((W == 0 || W >= 8) ? 2 : 4);
-  static __device__ __forceinline__ Vec16 get(const tccl_comm& c, const Args& a, int world, uint64_t vec) {
-    if (kNvls) return MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, vec));
-    Acc<T> acc;
-    acc.zero();
-#pragma unroll
-    for (int p = 0; p < kMaxW; ++p)
-      if (p < world) acc.add(ld_peer(vptr<T>(a.in[p], vec)));
-    return acc.pack();
-  }
+  static constexpr int U = kNvls ? 8 : ((W == 0 || W >= 8) ? 2 : 4);
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
     Entry sync(c, a.flags, bid);
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
     const uint64_t per = a.numel / world / VPT;  // vectors per rank
     const uint64_t lo = per * (uint64_t)c.rank;
-    const uint64_t nthr = (uint64_t)nb * blockDim.x;
-    const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
-    uint64_t i = tid;
+    const uint64_t bs = blockDim.x;
     if (kNvls) {
-      for (; i + (U - 1) * nthr < per; i += U * nthr) {
+      TCCL_FOR_SLABS(U, per, bid, nb, i0) {
         Vec16 v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i + u * nthr));
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * bs < per) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i0 + u * bs));
 #pragma unroll
-        for (int u = 0; u < U; ++u) st_local(vptr<T>(a.out, i + u * nthr), v[u]);
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * bs < per) st_local(vptr<T>(a.out, i0 + u * bs), v[u]);
       }
     } else {
-      for (; i + (U - 1) * nthr < per; i += U * nthr) {
+      TCCL_FOR_SLABS(U, per, bid, nb, i0) {
         Vec16 v[kMaxW][U];
 #pragma unroll
         for (int p = 0; p < kMaxW; ++p)
           if (p < world) {
 #pragma unroll
-            for (int u = 0; u < U; ++u) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i + u * nthr));
+            for (int u = 0; u < U; ++u)
+              if (i0 + u * bs < per) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i0 + u * bs));
           }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          Acc<T> acc;
-          acc.zero();
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * bs < per) {
+            Acc<T> acc;
+            acc.zero();
 #pragma unroll
-          for (int p = 0; p < kMaxW; ++p)
-            if (p < world) acc.add(v[p][u]);
-          st_local(vptr<T>(a.out, i + u * nthr), acc.pack());
-        }
+            for (int p = 0; p < kMaxW; ++p)
+              if (p < world) acc.add(v[p][u]);
+            st_local(vptr<T>(a.out, i0 + u * bs), acc.pack());
+          }
       }
     }
-    for (; i < per; i += nthr) st_local(vptr<T>(a.out, i), get(c, a, world, lo + i));
     sync.exit(c, a.flags, bid);
   }
 };

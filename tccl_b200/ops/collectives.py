@@ -207,7 +207,11 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
         a.mc_out = w.mc_ptr(dst)
         args[r] = a
     per_slice = -(-nvec // w.world_size)
-    grid = grid_for(w, per_slice, block, 4)
+    if algo == "twoshot_nvls":
+        cap = w.config.nvls_ctas if not w.config.max_ctas else None
+        grid = grid_for(w, per_slice, block, 8, cap=cap)
+    else:
+        grid = grid_for(w, per_slice, block, 2 if w.world_size >= 8 else 4)
     return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt), args, result=dst)
 
 
