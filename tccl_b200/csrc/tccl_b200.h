@@ -154,6 +154,18 @@ typedef struct tccl_tree_args {
 } tccl_tree_args;
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
 
+/* ---- tcgen05 GEMM (bf16 in, fp32 accumulate in tensor memory, bf16 out) ---- */
+typedef struct tccl_gemm_args {
+  const void* a;   /* [m, k], k contiguous, lda elements between rows */
+  const void* bt;  /* [n, k], k contiguous (the layout of a torch Linear weight) */
+  void* c;         /* [m, n] */
+  void* status;    /* optional: TCCL_ST_WORDS uint32 words for a timeout report, or NULL */
+  int32_t m, n, k;
+  int32_t lda, ldb, ldc;
+} tccl_gemm_args;
+/* c = a * bt^T on this GPU; grid <= 0 picks one CTA per SM */
+int tccl_gemm_bf16(const tccl_gemm_args*, int grid, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,36 @@
+"""Stand-alone tcgen05 GEMM (``c = a @ bt.T``), the mainloop the fused
+collective kernels are built on.  bf16 operands, fp32 accumulation in tensor
+memory, bf16 result."""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..utils import lib as L
+
+__all__ = ["gemm_bf16"]
+
+
+def gemm_bf16(a: torch.Tensor, bt: torch.Tensor, out: Optional[torch.Tensor] = None, *, ctas: int = 0,
+              status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[m, n] = sum_k a[m, k] * bt[n, k]`` on the current GPU.
+
+    ``a`` is ``[M, K]`` and ``bt`` is ``[N, K]`` (the layout of ``nn.Linear.weight``),
+    both bf16 with a unit inner stride; ``K`` and ``N`` must be multiples of 8."""
+    if a.dtype != torch.bfloat16 or bt.dtype != torch.bfloat16:
+        raise TypeError("gemm_bf16 takes bfloat16 operands")
+    if a.dim() != 2 or bt.dim() != 2 or a.shape[1] != bt.shape[1]:
+        raise ValueError("shapes must be a[M, K], bt[N, K]")
+    if a.stride(1) != 1 or bt.stride(1) != 1:
+        raise ValueError("operands must have a unit inner stride")
+    M, K = a.shape
+    N = bt.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    g = L.GemmArgs(a.data_ptr(), bt.data_ptr(), out.data_ptr(), status.data_ptr() if status is not None else 0,
+                   M, N, K, a.stride(0), bt.stride(0), out.stride(0))
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    L.check(L.lib().tccl_gemm_bf16(C.byref(g), int(ctas), C.c_void_p(stream)), "tccl_gemm_bf16")
+    return out

@@ -98,6 +98,14 @@ class TreeArgs(C.Structure):
     ]
 
 
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_uint64), ("bt", C.c_uint64), ("c", C.c_uint64), ("status", C.c_uint64),
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("lda", C.c_int32), ("ldb", C.c_int32), ("ldc", C.c_int32),
+    ]
+
+
 class Launch(C.Structure):
     _fields_ = [
         ("grid", C.c_int32),
