@@ -9,6 +9,7 @@ namespace tccl {
 namespace gemm {
 
 struct PlainPolicy {
+  const CUtensorMap* map_a;
   __nv_bfloat16* C;
   int M, N, ldc;
   int tiles_n, total;
@@ -20,6 +21,10 @@ struct PlainPolicy {
     return true;
   }
   __device__ __forceinline__ bool before_load(int, int, const Abort&) const { return true; }
+  __device__ __forceinline__ void a_tile(int mt, const CUtensorMap*& map, int& y) const {
+    map = map_a;
+    y = mt * BM;
+  }
   __device__ __forceinline__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort&) const {
     const int row = mt * BM + quad * 32 + lane;
     __nv_bfloat16* crow = C + (size_t)row * ldc;
@@ -45,7 +50,8 @@ gemm_plain_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   // a private tccl_comm-free run: status words are optional
   tccl_comm fake;
   fake.local = status ? status - TCCL_LOCAL_STATUS : nullptr;
-  run_mainloop(&map_a, &map_b, shp, pol, status ? &fake : nullptr, 2000000000ull);
+  pol.map_a = &map_a;
+  run_mainloop(&map_b, shp, pol, status ? &fake : nullptr, 2000000000ull);
 }
 
 }  // namespace gemm
@@ -63,6 +69,7 @@ extern "C" int tccl_gemm_bf16(const tccl_gemm_args* g, int grid, void* stream) {
   rc = make_tmap_bf16_kmajor(&mb, g->bt, g->n, g->k, g->ldb, BN);
   if (rc) return rc;
   PlainPolicy pol;
+  pol.map_a = nullptr;
   pol.C = reinterpret_cast<__nv_bfloat16*>(g->c);
   pol.M = g->m;
   pol.N = g->n;

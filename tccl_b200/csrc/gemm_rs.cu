@@ -1,0 +1,232 @@
+// GEMM -> reduce-scatter in ONE kernel (tensor parallel down-projection):
+//   out_r[M/W, N] = rows [r M/W, (r+1) M/W) of  sum_src  A_src[M, K_src] * Bt_src[N, K_src]^T
+// Every rank runs the tcgen05 mainloop over all M x N tiles of its partial
+// product.  Tiles are ordered by owner, starting with the next rank and ending
+// with the own rows.  The epilogue of a tile owned by a peer stores the bf16
+// partial straight into that peer's staging slot [src][tile] over NVLink
+// (posted 16-byte stores, fully coalesced) and then raises the tile's flag with
+// a release store.  The epilogue of an own tile — computed last, when the peers'
+// partials have mostly landed — waits for the W-1 flags of that tile, adds the
+// W-1 staged partials to its own fp32 accumulator from tensor memory, rounds
+// once and writes the final rows.  The transfer of tile i therefore overlaps
+// the MMAs of tile i+1 (second TMEM accumulator) tile by tile, and the
+// reduction costs no extra kernel and no extra pass over HBM.
+//
+// Flags carry the call's epoch (kept in device memory and advanced by the last
+// CTA to finish), so nothing has to be reset and a captured graph can replay.
+// The entry barrier keeps a fast rank from overwriting a staging slot that a
+// slow rank is still reducing from the previous call.
+#include "gemm_host.cuh"
+#include "gemm_tcgen05.cuh"
+
+namespace tccl {
+namespace gemm {
+
+constexpr uint32_t kSlotBytes = BM * BN * 2;  // one bf16 tile
+
+struct alignas(64) GemmRsParams {
+  CUtensorMap map_a, map_b;
+  Shape shp;
+  __nv_bfloat16* out;
+  int ldo;
+  int tiles_n;
+  int tiles_m_per_rank;
+};
+
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+struct GemmRsPolicy {
+  const tccl_comm* c;
+  const GemmRsParams* p;
+  int bid, nb;
+  uint32_t epoch;
+  int tpo;  // tiles per owner
+
+  __device__ __forceinline__ bool tile(int i, int& mt, int& nt) const {
+    const int t = bid + i * nb;
+    if (t >= c->world * tpo) return false;
+    const int j = t / tpo, local = t - j * tpo;
+    int owner = c->rank + 1 + j;
+    if (owner >= c->world) owner -= c->world;
+    mt = owner * p->tiles_m_per_rank + local / p->tiles_n;
+    nt = local % p->tiles_n;
+    return true;
+  }
+  __device__ __forceinline__ bool before_load(int, int, const Abort&) const { return true; }
+  __device__ __forceinline__ void a_tile(int mt, const CUtensorMap*& map, int& y) const {
+    map = &p->map_a;
+    y = mt * BM;
+  }
+  // byte offset of (row, 32-column group cg, 16-byte vector v) inside a staging slot:
+  // for fixed (cg, v) the 128 rows are contiguous, so a warp's store is one 512-byte run
+  static __device__ __forceinline__ uint32_t slot_off(int row, int cg, int v) {
+    return (uint32_t)(((cg * 4 + v) * BM + row) * 16);
+  }
+
+  __device__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort& ab) const {
+    const int W = c->world, me = c->rank;
+    const int owner = mt / p->tiles_m_per_rank;
+    const int lt = (mt - owner * p->tiles_m_per_rank) * p->tiles_n + nt;
+    const int row = quad * 32 + lane;
+    if (owner != me) {
+      char* slot = c->stage[owner] + ((size_t)me * tpo + lt) * kSlotBytes;
+#pragma unroll 1
+      for (int cg = 0; cg < BN / 32; ++cg) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + cg * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int v = 0; v < 4; ++v) st_peer(slot + slot_off(row, cg, v), pack8_bf16(r + v * 8));
+      }
+      epi_bar();  // all 128 threads' stores are issued before the release below
+      if (quad == 0 && lane == 0)
+        st_release_sys(c->flags[owner] + TCCL_FLAG_TILE + me * TCCL_MAX_TILES + lt, epoch);
+      return true;
+    }
+    // own tile: gather the peers' partials
+    if (quad == 0 && lane < W && lane != me) {
+      if (!wait_reach(c->flags[me] + TCCL_FLAG_TILE + lane * TCCL_MAX_TILES + lt, epoch, *c, ab.deadline, lane,
+                      TCCL_W_TILE))
+        *ab.flag = 1;
+    }
+    epi_bar();
+    if (*ab.flag) return false;
+    const int orow = (mt - owner * p->tiles_m_per_rank) * BM + row;
+    __nv_bfloat16* dst = p->out + (size_t)orow * p->ldo + nt * BN;
+    const bool row_ok = mt * BM + row < p->shp.M;
+#pragma unroll 1
+    for (int cg = 0; cg < BN / 32; ++cg) {
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + cg * 32, r);
+      tmem_ld_wait();
+      float acc[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]);
+      for (int src = 0; src < W; ++src) {
+        if (src == me) continue;
+        const char* slot = c->stage[me] + ((size_t)src * tpo + lt) * kSlotBytes;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const Vec16 x = ld_peer(slot + slot_off(row, cg, v));
+          acc[v * 8 + 0] += Acc<__nv_bfloat16>::lo(x.x); acc[v * 8 + 1] += Acc<__nv_bfloat16>::hi(x.x);
+          acc[v * 8 + 2] += Acc<__nv_bfloat16>::lo(x.y); acc[v * 8 + 3] += Acc<__nv_bfloat16>::hi(x.y);
+          acc[v * 8 + 4] += Acc<__nv_bfloat16>::lo(x.z); acc[v * 8 + 5] += Acc<__nv_bfloat16>::hi(x.z);
+          acc[v * 8 + 6] += Acc<__nv_bfloat16>::lo(x.w); acc[v * 8 + 7] += Acc<__nv_bfloat16>::hi(x.w);
+        }
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          if (nt * BN + cg * 32 + v * 8 < p->shp.N) {
+            Vec16 o;
+            o.x = Acc<__nv_bfloat16>::pk(acc[v * 8 + 0], acc[v * 8 + 1]);
+            o.y = Acc<__nv_bfloat16>::pk(acc[v * 8 + 2], acc[v * 8 + 3]);
+            o.z = Acc<__nv_bfloat16>::pk(acc[v * 8 + 4], acc[v * 8 + 5]);
+            o.w = Acc<__nv_bfloat16>::pk(acc[v * 8 + 6], acc[v * 8 + 7]);
+            st_local(dst + cg * 32 + v * 8, o);
+          }
+        }
+      }
+    }
+    return true;
+  }
+};
+
+__device__ __forceinline__ void gemm_rs_body(const tccl_comm& c, const GemmRsParams& p, int bid, int nb) {
+  const uint64_t deadline = globaltimer() + c.timeout_ns;
+  GemmRsPolicy pol;
+  pol.c = &c;
+  pol.p = &p;
+  pol.bid = bid;
+  pol.nb = nb;
+  pol.epoch = c.local[TCCL_LOCAL_TILE_EPOCH] + 1u;
+  pol.tpo = p.tiles_m_per_rank * p.tiles_n;
+  barrier_p2p(c, bid, deadline);  // the previous call's staging slots are free on every rank
+  if (threadIdx.x == 0) tma_prefetch_desc(&p.map_a);
+  run_mainloop(&p.map_b, p.shp, pol, &c, c.timeout_ns);
+  // the last CTA of this rank to finish publishes the new epoch for the next call
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_SCHED, 1u);
+    if (done == (uint32_t)nb - 1u) {
+      c.local[TCCL_LOCAL_SCHED] = 0u;
+      c.local[TCCL_LOCAL_TILE_EPOCH] = pol.epoch;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_rs_kernel(const __grid_constant__ tccl_comm comm, const __grid_constant__ GemmRsParams p) {
+  gemm_rs_body(comm, p, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(kThreads, 1) gemm_rs_kernel_emu(const tccl_comm* comms, const GemmRsParams* ps) {
+  gemm_rs_body(comms[blockIdx.y], ps[blockIdx.y], blockIdx.x, gridDim.x);
+}
+
+static int fill_params(GemmRsParams* p, const tccl_gemm_rs_args* g, int world) {
+  if (g->m <= 0 || g->n <= 0 || g->k <= 0) return -TCCL_EINVAL;
+  if ((g->lda % 8) || (g->ldb % 8) || (g->ldo % 8) || (g->k % 8) || (g->n % BN)) return -TCCL_EALIGN;
+  if (g->m % (world * BM)) return -TCCL_ESIZE;  // every rank owns whole 128-row tiles
+  if (((uintptr_t)g->a | (uintptr_t)g->bt | (uintptr_t)g->out) & 15) return -TCCL_EALIGN;
+  int rc = make_tmap_bf16_kmajor(&p->map_a, g->a, g->m, g->k, g->lda, BM);
+  if (rc) return rc;
+  rc = make_tmap_bf16_kmajor(&p->map_b, g->bt, g->n, g->k, g->ldb, BN);
+  if (rc) return rc;
+  p->shp = Shape{g->m, g->n, g->k};
+  p->out = reinterpret_cast<__nv_bfloat16*>(g->out);
+  p->ldo = g->ldo;
+  p->tiles_n = g->n / BN;
+  p->tiles_m_per_rank = g->m / world / BM;
+  if (p->tiles_n * p->tiles_m_per_rank > TCCL_MAX_TILES) return -TCCL_ESIZE;
+  return 0;
+}
+
+}  // namespace gemm
+}  // namespace tccl
+
+using namespace tccl::gemm;
+
+extern "C" uint64_t tccl_gemm_rs_stage_bytes(int m, int n, int world) {
+  return (uint64_t)world * (uint64_t)(m / world / BM) * (uint64_t)(n / BN) * kSlotBytes;
+}
+extern "C" uint64_t tccl_gemm_rs_param_bytes(void) { return sizeof(GemmRsParams); }
+
+// real mode: `comm` and `args` are host structs of the calling rank, `dev_params` unused.
+// emulated mode: `comm` is the device array of W communicators, `args` a HOST array of W
+// argument structs, `dev_params` device scratch of W * tccl_gemm_rs_param_bytes() bytes
+// (64-byte aligned) that receives the kernels' parameter blocks.
+extern "C" int tccl_gemm_reduce_scatter(const tccl_comm* comm, const tccl_gemm_rs_args* args, void* dev_params,
+                                        uint64_t stage_bytes, const tccl_launch* l) {
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(l->stream);
+  if (l->grid <= 0) return -TCCL_EINVAL;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_rs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_rs_kernel_emu, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  if (l->n_emu == 0) {
+    GemmRsParams p;
+    int rc = fill_params(&p, args, comm->world);
+    if (rc) return rc;
+    if (tccl_gemm_rs_stage_bytes(args->m, args->n, comm->world) > comm->stage_bytes) return -TCCL_ESIZE;
+    gemm_rs_kernel<<<l->grid, kThreads, kSmemBytes, s>>>(*comm, p);
+    return (int)cudaGetLastError();
+  }
+  const int W = l->n_emu;
+  if (W < 1 || W > TCCL_MAX_WORLD || !dev_params || ((uintptr_t)dev_params & 63)) return -TCCL_EINVAL;
+  if (tccl_gemm_rs_stage_bytes(args[0].m, args[0].n, W) > stage_bytes) return -TCCL_ESIZE;
+  GemmRsParams ps[TCCL_MAX_WORLD];
+  for (int r = 0; r < W; ++r) {
+    int rc = fill_params(&ps[r], &args[r], W);
+    if (rc) return rc;
+  }
+  cudaError_t e = cudaMemcpyAsync(dev_params, ps, sizeof(GemmRsParams) * W, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return (int)e;
+  const GemmRsParams* dps = reinterpret_cast<const GemmRsParams*>(dev_params);
+  void* kargs[2] = {(void*)&comm, (void*)&dps};
+  return (int)cudaLaunchCooperativeKernel((const void*)gemm_rs_kernel_emu, dim3(l->grid, W), dim3(kThreads), kargs,
+                                          kSmemBytes, s);
+}

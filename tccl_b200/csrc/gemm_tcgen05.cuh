@@ -185,13 +185,14 @@ struct SmemLayout {
 
 // A schedule maps the i-th tile of this CTA to (m_tile, n_tile); hooks:
 //   Policy::tile(i, m_tile, n_tile)          -> false when the CTA is out of tiles
+//   Policy::a_tile(m_tile, map, y)           -> which tensor map / row coordinate holds the A rows
 //   Policy::before_load(m_tile, n_tile, ab)  -> runs in the producer thread before the
 //                                               tile's first TMA load (wait for remote rows)
 //   Policy::epilogue(m_tile, n_tile, acc_taddr, quad, lane, ab)
 //                                            -> runs in the 4 epilogue warps
 template <class Policy>
-__device__ void run_mainloop(const CUtensorMap* map_a, const CUtensorMap* map_b, const Shape shp, Policy& pol,
-                             const tccl_comm* comm, uint64_t timeout_ns) {
+__device__ void run_mainloop(const CUtensorMap* map_b, const Shape shp, Policy& pol, const tccl_comm* comm,
+                             uint64_t timeout_ns) {
   extern __shared__ uint8_t smem_raw[];
   SmemLayout sm(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -208,7 +209,6 @@ __device__ void run_mainloop(const CUtensorMap* map_a, const CUtensorMap* map_b,
       mbar_init(sm.tmem_empty + i, 4 * 32);
     }
     fence_barrier_init();
-    tma_prefetch_desc(map_a);
     tma_prefetch_desc(map_b);
   }
   if (warp == 2) {
@@ -229,13 +229,16 @@ __device__ void run_mainloop(const CUtensorMap* map_a, const CUtensorMap* map_b,
       int mt, nt;
       for (int i = 0; ok && pol.tile(i, mt, nt); ++i) {
         ok = pol.before_load(mt, nt, ab);
+        const CUtensorMap* map_a;
+        int ya;
+        pol.a_tile(mt, map_a, ya);
         for (int kb = 0; ok && kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           ok = mbar_wait(sm.empty + s, ph ^ 1, ab);
           if (!ok) break;
           mbar_arrive_expect_tx(sm.full + s, kStageBytes);
-          tma_load_2d(sm.a[s], map_a, sm.full + s, kb * BK, mt * BM);
+          tma_load_2d(sm.a[s], map_a, sm.full + s, kb * BK, ya);
           tma_load_2d(sm.b[s], map_b, sm.full + s, kb * BK, nt * BN);
         }
       }

@@ -166,6 +166,23 @@ typedef struct tccl_gemm_args {
 /* c = a * bt^T on this GPU; grid <= 0 picks one CTA per SM */
 int tccl_gemm_bf16(const tccl_gemm_args*, int grid, void* stream);
 
+/* ---- fused GEMM -> reduce-scatter (rows scattered over the ranks) ---------- */
+typedef struct tccl_gemm_rs_args {
+  const void* a;   /* this rank's [m, k] activations (its K-slice), k contiguous */
+  const void* bt;  /* this rank's [n, k] weight slice, k contiguous */
+  void* out;       /* this rank's [m / world, n] result rows */
+  int32_t m, n, k; /* m % (world * 128) == 0, n % 256 == 0, k % 8 == 0 */
+  int32_t lda, ldb, ldo;
+} tccl_gemm_rs_args;
+/* bytes of staging area (per rank) the fused kernel needs for an m x n product */
+uint64_t tccl_gemm_rs_stage_bytes(int m, int n, int world);
+uint64_t tccl_gemm_rs_param_bytes(void);
+/* real mode: comm/args are host structs, dev_params unused.  Emulated mode: comm is the
+ * device array of communicators, args a HOST array of n_emu structs, dev_params device
+ * scratch of n_emu * tccl_gemm_rs_param_bytes() bytes (64-byte aligned). */
+int tccl_gemm_reduce_scatter(const tccl_comm* comm, const tccl_gemm_rs_args* args, void* dev_params,
+                             uint64_t stage_bytes, const tccl_launch* l);
+
 #ifdef __cplusplus
 }
 #endif

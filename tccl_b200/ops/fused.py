@@ -1,0 +1,94 @@
+"""Fused compute + collective ops for tensor parallelism (the "extensible
+collectives" the reference names as its motivation on slide 4 but does not
+implement): GEMM -> reduce-scatter, all-gather -> GEMM, and all-reduce + bias +
+residual + RMSNorm.  Each is ONE kernel in which the tensor-core tiles
+(tcgen05 / TMEM, fed by TMA from local memory) and the peer traffic (P2P or
+NVLS stores / loads over NVLink) overlap tile by tile.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from ..parallel.world import WorldBase
+from ..utils import lib as L
+from ._common import K, get_world
+
+__all__ = ["gemm_reduce_scatter"]
+
+
+def _locals(w: WorldBase, x):
+    """Per-rank local tensors of an ordinary (non symmetric) argument: a tensor in
+    a real world, a list/EmuTensor of W tensors in an emulated one."""
+    if w.plans is not None:  # a real world drives exactly one rank
+        return {w.local_ranks[0]: x}
+    return {r: x[r] for r in w.local_ranks}
+
+
+def _gemm_ctas(w: WorldBase) -> int:
+    n = w.config.max_ctas or w.num_sms()
+    if w.plans is None:  # emulated ranks share one GPU and each CTA takes a whole SM
+        n = max(1, w.num_sms() // w.world_size)
+    return n
+
+
+def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
+    """``out_r = rows r of sum_ranks (a_rank @ bt_rank.T)`` — tensor-parallel
+    down-projection fused with the reduce-scatter over token rows.
+
+    ``a``: this rank's ``[M, K_r]`` activations (its slice of the contraction
+    dimension), ``bt``: its ``[N, K_r]`` weight slice (``nn.Linear`` layout), both
+    bf16.  Returns this rank's ``[M / W, N]`` rows.  ``M % (128 W) == 0`` and
+    ``N % 256 == 0``.  Inputs and output are ordinary tensors; the partial tiles
+    travel through the communicator's symmetric staging area."""
+    w = get_world(world)
+    W = w.world_size
+    As, Bs = _locals(w, a), _locals(w, bt)
+    a0, b0 = As[w.local_ranks[0]], Bs[w.local_ranks[0]]
+    if a0.dtype != torch.bfloat16 or b0.dtype != torch.bfloat16:
+        raise TypeError("gemm_reduce_scatter takes bfloat16 operands")
+    M, Kr = a0.shape
+    N = b0.shape[0]
+    if b0.shape[1] != Kr:
+        raise ValueError("a is [M, K], bt is [N, K]")
+    if M % (W * 128) or N % 256 or Kr % 8:
+        raise ValueError(f"need M % {W * 128} == 0, N % 256 == 0, K % 8 == 0 (got M={M}, N={N}, K={Kr})")
+    lib = L.lib()
+    lib.tccl_gemm_rs_stage_bytes.restype = C.c_uint64
+    lib.tccl_gemm_rs_param_bytes.restype = C.c_uint64
+    need = lib.tccl_gemm_rs_stage_bytes(M, N, W)
+    stage_bytes = w.config.stage_mb << 20
+    if need > stage_bytes:
+        raise ValueError(f"staging area too small: need {need >> 20} MiB, have {w.config.stage_mb} MiB "
+                         "(raise TCCL_STAGE_MB)")
+    outs = {}
+    Os = _locals(w, out) if out is not None else None
+    arr = (L.GemmRsArgs * len(w.local_ranks))()
+    for i, r in enumerate(w.local_ranks):
+        ar, br = As[r], Bs[r]
+        if ar.stride(1) != 1 or br.stride(1) != 1:
+            raise ValueError("operands must have a unit inner stride")
+        o = Os[r] if Os is not None else torch.empty((M // W, N), dtype=torch.bfloat16, device=ar.device)
+        outs[r] = o
+        arr[i] = L.GemmRsArgs(ar.data_ptr(), br.data_ptr(), o.data_ptr(), M, N, Kr, ar.stride(0), br.stride(0),
+                              o.stride(0))
+    stream = torch.cuda.current_stream(a0.device).cuda_stream
+    grid = _gemm_ctas(w)
+    fn = lib.tccl_gemm_reduce_scatter
+    if w.plans is not None:
+        l = L.Launch(grid, 256, 0, 0, C.c_void_p(stream))
+        rc = fn(C.byref(w.comm), C.byref(arr[0]), None, C.c_uint64(stage_bytes), C.byref(l))
+    else:
+        pb = int(lib.tccl_gemm_rs_param_bytes())
+        scratch = torch.empty(pb * W + 64, dtype=torch.uint8, device=a0.device)
+        base = (scratch.data_ptr() + 63) & ~63
+        w._keep.append(scratch)
+        l = L.Launch(grid, 256, W, 0, C.c_void_p(stream))
+        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), arr, C.c_void_p(base), C.c_uint64(stage_bytes), C.byref(l))
+    L.check(rc, "tccl_gemm_reduce_scatter")
+    w.launches += 1
+    if out is not None:
+        return out
+    return [outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]]

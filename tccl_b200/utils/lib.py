@@ -106,6 +106,14 @@ class GemmArgs(C.Structure):
     ]
 
 
+class GemmRsArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_uint64), ("bt", C.c_uint64), ("out", C.c_uint64),
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("lda", C.c_int32), ("ldb", C.c_int32), ("ldo", C.c_int32),
+    ]
+
+
 class Launch(C.Structure):
     _fields_ = [
         ("grid", C.c_int32),

@@ -1,0 +1,34 @@
+"""Fused compute + collective kernels with emulated ranks, against an fp32
+single-GPU PyTorch reference of the same operands."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+
+@pytest.mark.parametrize("W,M,N,K", [(1, 256, 256, 128), (2, 256, 256, 64), (2, 512, 512, 1792), (4, 1024, 512, 448),
+                                     (8, 1024, 256, 224), (4, 2048, 1024, 1792)])
+def test_gemm_reduce_scatter(emu_worlds, W, M, N, K):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    a = [_rand((M, K), 4000 + r) for r in range(W)]
+    bt = [_rand((N, K), 5000 + r, 0.02) for r in range(W)]
+    for rep in range(2):  # twice: the tile epochs must advance together
+        outs = tccl.gemm_reduce_scatter(a, bt, world=w)
+        torch.cuda.synchronize()
+        w.check()
+        ref = sum(a[r].float() @ bt[r].float().t() for r in range(W))
+        rows = M // W
+        for r in range(W):
+            got = outs[r].float()
+            exp = ref[r * rows:(r + 1) * rows]
+            err = (got - exp).abs()
+            # W-1 partials travel as bf16 (each rounded once), then one final rounding
+            bound = exp.abs() * 2 ** -8 + 2 ** -8 * W * 0.02 * (K ** 0.5) * 3 + 1e-3
+            assert bool((err <= bound).all()), f"rank {r}: max err {err.max().item()} ratio {(err / bound).max().item()}"
