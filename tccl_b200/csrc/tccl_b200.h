@@ -35,15 +35,18 @@ extern "C" {
 #define TCCL_FLAG_TILE (TCCL_FLAG_TREE_DOWN + 2 * TCCL_TREE_MAX_CTAS)  /* [src][tile] GEMM */
 #define TCCL_MAX_TILES 4096
 #define TCCL_FLAG_LL (TCCL_FLAG_TILE + TCCL_MAX_WORLD * TCCL_MAX_TILES) /* misc / p2p */
-#define TCCL_FLAG_WORDS (TCCL_FLAG_LL + 1024)
+#define TCCL_FLAG_AG (TCCL_FLAG_LL + 1024)                            /* [src][row tile] AG->GEMM */
+#define TCCL_MAX_ROW_TILES 256
+#define TCCL_FLAG_WORDS (TCCL_FLAG_AG + TCCL_MAX_WORLD * TCCL_MAX_ROW_TILES)
 
 /* local (non peer-visible) state, in 32-bit words */
 #define TCCL_LOCAL_EPOCH 0                                       /* [block] p2p barrier   */
 #define TCCL_LOCAL_MCEPOCH (TCCL_LOCAL_EPOCH + TCCL_MAX_BLOCKS)  /* [block] nvls barrier  */
 #define TCCL_LOCAL_STATUS (TCCL_LOCAL_MCEPOCH + TCCL_MAX_BLOCKS) /* tccl_status_word      */
 #define TCCL_LOCAL_TILE_EPOCH (TCCL_LOCAL_STATUS + 16)           /* 1 word: tile epoch    */
-#define TCCL_LOCAL_SCHED (TCCL_LOCAL_TILE_EPOCH + 1)             /* scheduler counters    */
-#define TCCL_LOCAL_WORDS (TCCL_LOCAL_SCHED + 63)
+#define TCCL_LOCAL_SCHED (TCCL_LOCAL_TILE_EPOCH + 1)             /* [0] CTAs of a fused kernel that are done */
+#define TCCL_LOCAL_AGCNT (TCCL_LOCAL_SCHED + 63)                 /* [row tile] data movers done (AG->GEMM) */
+#define TCCL_LOCAL_WORDS (TCCL_LOCAL_AGCNT + TCCL_MAX_ROW_TILES)
 
 enum tccl_status_word {
   TCCL_ST_CODE = 0,   /* 0 = ok, else tccl_error */
@@ -182,6 +185,22 @@ uint64_t tccl_gemm_rs_param_bytes(void);
  * scratch of n_emu * tccl_gemm_rs_param_bytes() bytes (64-byte aligned). */
 int tccl_gemm_reduce_scatter(const tccl_comm* comm, const tccl_gemm_rs_args* args, void* dev_params,
                              uint64_t stage_bytes, const tccl_launch* l);
+
+/* ---- fused all-gather -> GEMM (rows gathered over the ranks) -------------- */
+typedef struct tccl_ag_gemm_args {
+  const void* a_shard;              /* this rank's [m / world, k] rows, k contiguous */
+  void* a_full[TCCL_MAX_WORLD];     /* every rank's gathered [m, k] buffer (symmetric, peer-mapped) */
+  void* mc_a_full;                  /* multicast alias of the gathered buffer, or NULL */
+  const void* bt;                   /* this rank's [n, k] weight slice, k contiguous */
+  void* out;                        /* this rank's [m, n] result */
+  int32_t m, n, k;                  /* m % (world * 128) == 0, n % 8 == 0, k % 8 == 0 */
+  int32_t lda_shard, lda_full, ldb, ldo;
+  int32_t comm_ctas;                /* CTAs that move the shard; the others run the GEMM */
+} tccl_ag_gemm_args;
+uint64_t tccl_ag_gemm_param_bytes(void);
+/* same calling convention as tccl_gemm_reduce_scatter */
+int tccl_allgather_gemm(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,
+                        const tccl_launch* l);
 
 #ifdef __cplusplus
 }

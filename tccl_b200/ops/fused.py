@@ -16,7 +16,7 @@ from ..parallel.world import WorldBase
 from ..utils import lib as L
 from ._common import K, get_world
 
-__all__ = ["gemm_reduce_scatter"]
+__all__ = ["gemm_reduce_scatter", "all_gather_gemm"]
 
 
 def _locals(w: WorldBase, x):
@@ -92,3 +92,77 @@ def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
     if out is not None:
         return out
     return [outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]]
+
+
+def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, world: Optional[WorldBase] = None):
+    """``out_r = all_gather(a_shard) @ bt_r.T`` — tensor-parallel up-projection
+    fused with the all-gather of the token rows.
+
+    ``a_shard``: this rank's ``[M / W, K]`` rows (bf16, any device memory), ``bt``:
+    its ``[N_r, K]`` weight slice.  ``a_full`` is the ``[M, K]`` gathered buffer in
+    symmetric memory (allocated and cached per shape when omitted); it holds the
+    gathered activations afterwards.  Returns ``(out, a_full)`` with ``out`` the
+    rank's ``[M, N_r]`` result.  ``M % (128 W) == 0``."""
+    w = get_world(world)
+    W = w.world_size
+    As, Bs = _locals(w, a_shard), _locals(w, bt)
+    a0, b0 = As[w.local_ranks[0]], Bs[w.local_ranks[0]]
+    if a0.dtype != torch.bfloat16 or b0.dtype != torch.bfloat16:
+        raise TypeError("all_gather_gemm takes bfloat16 operands")
+    rows, Kd = a0.shape
+    M, N = rows * W, b0.shape[0]
+    if b0.shape[1] != Kd:
+        raise ValueError("a_shard is [M / W, K], bt is [N, K]")
+    if rows % 128 or N % 8 or Kd % 8:
+        raise ValueError(f"need (M / W) % 128 == 0, N % 8 == 0, K % 8 == 0 (got M/W={rows}, N={N}, K={Kd})")
+    if a_full is None:
+        cache = w.__dict__.setdefault("_ag_buffers", {})
+        a_full = cache.get((M, Kd))
+        if a_full is None:
+            a_full = cache[(M, Kd)] = w.empty((M, Kd), torch.bfloat16)
+    full_ptrs = w.peer_ptrs(a_full)
+    mc = w.mc_ptr(a_full)
+    lib = L.lib()
+    lib.tccl_ag_gemm_param_bytes.restype = C.c_uint64
+    grid = _gemm_ctas(w)
+    if comm_ctas <= 0:
+        tiles = (M // 128) * -(-N // 256)
+        # give the data movers the CTAs the last GEMM wave would leave idle anyway
+        waves = -(-tiles // max(1, grid - 8))
+        comm_ctas = max(2 if grid <= 16 else 8, min(grid // 4, grid - -(-tiles // waves)))
+        comm_ctas = max(1, min(comm_ctas, grid - 1))
+    outs = {}
+    Os = _locals(w, out) if out is not None else None
+    arr = (L.AgGemmArgs * len(w.local_ranks))()
+    for i, r in enumerate(w.local_ranks):
+        ar, br = As[r], Bs[r]
+        if ar.stride(1) != 1 or br.stride(1) != 1:
+            raise ValueError("operands must have a unit inner stride")
+        o = Os[r] if Os is not None else torch.empty((M, N), dtype=torch.bfloat16, device=ar.device)
+        outs[r] = o
+        g = L.AgGemmArgs()
+        g.a_shard = ar.data_ptr()
+        for q, v in enumerate(full_ptrs):
+            g.a_full[q] = v
+        g.mc_a_full = mc
+        g.bt, g.out = br.data_ptr(), o.data_ptr()
+        g.m, g.n, g.k = M, N, Kd
+        g.lda_shard, g.lda_full, g.ldb, g.ldo = ar.stride(0), Kd, br.stride(0), o.stride(0)
+        g.comm_ctas = comm_ctas
+        arr[i] = g
+    stream = torch.cuda.current_stream(a0.device).cuda_stream
+    fn = lib.tccl_allgather_gemm
+    if w.plans is not None:
+        l = L.Launch(grid, 256, 0, 0, C.c_void_p(stream))
+        rc = fn(C.byref(w.comm), C.byref(arr[0]), None, C.byref(l))
+    else:
+        pb = int(lib.tccl_ag_gemm_param_bytes())
+        scratch = torch.empty(pb * W + 64, dtype=torch.uint8, device=a0.device)
+        base = (scratch.data_ptr() + 63) & ~63
+        w._keep.append(scratch)
+        l = L.Launch(grid, 256, W, 0, C.c_void_p(stream))
+        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), arr, C.c_void_p(base), C.byref(l))
+    L.check(rc, "tccl_allgather_gemm")
+    w.launches += 1
+    res = out if out is not None else ([outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]])
+    return res, a_full

@@ -114,6 +114,16 @@ class GemmRsArgs(C.Structure):
     ]
 
 
+class AgGemmArgs(C.Structure):
+    _fields_ = [
+        ("a_shard", C.c_uint64), ("a_full", C.c_uint64 * MAX_WORLD), ("mc_a_full", C.c_uint64),
+        ("bt", C.c_uint64), ("out", C.c_uint64),
+        ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+        ("lda_shard", C.c_int32), ("lda_full", C.c_int32), ("ldb", C.c_int32), ("ldo", C.c_int32),
+        ("comm_ctas", C.c_int32),
+    ]
+
+
 class Launch(C.Structure):
     _fields_ = [
         ("grid", C.c_int32),

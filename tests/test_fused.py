@@ -32,3 +32,25 @@ def test_gemm_reduce_scatter(emu_worlds, W, M, N, K):
             # W-1 partials travel as bf16 (each rounded once), then one final rounding
             bound = exp.abs() * 2 ** -8 + 2 ** -8 * W * 0.02 * (K ** 0.5) * 3 + 1e-3
             assert bool((err <= bound).all()), f"rank {r}: max err {err.max().item()} ratio {(err / bound).max().item()}"
+
+
+@pytest.mark.parametrize("W,M,N,K", [(1, 256, 256, 128), (2, 256, 512, 64), (2, 1024, 1792, 512), (4, 1024, 264, 448),
+                                     (8, 1024, 256, 256), (4, 2048, 1792, 1024)])
+def test_all_gather_gemm(emu_worlds, W, M, N, K):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    rows = M // W
+    shards = [_rand((rows, K), 4000 + r) for r in range(W)]
+    bt = [_rand((N, K), 5000 + r, 0.02) for r in range(W)]
+    a_all = torch.cat(shards).float()
+    for rep in range(2):
+        outs, a_full = tccl.all_gather_gemm(shards, bt, world=w)
+        torch.cuda.synchronize()
+        w.check()
+        for r in range(W):
+            ref = a_all @ bt[r].float().t()
+            err = (outs[r].float() - ref).abs()
+            bound = ref.abs() * 2 ** -8 + 1e-3 * (K ** 0.5) * 0.02
+            assert bool((err <= bound).all()), f"rank {r}: max err {err.max().item()} ratio {(err / bound).max().item()}"
+            assert torch.equal(a_full[r].float(), a_all)  # the gathered activations are left behind, exactly
