@@ -1,0 +1,149 @@
+// all-reduce + bias + residual add + RMSNorm in ONE kernel (two-shot over token
+// rows): rank r owns rows [r T/W, (r+1) T/W).  For each owned row a CTA sums the
+// W partial rows (multimem.ld_reduce through the switch, or W peer loads with
+// fp32 accumulation), adds bias and residual, reduces sum(v^2) over the row in
+// the CTA, scales by rsqrt(mean + eps) * weight and stores the normalised row to
+// EVERY rank's output (one multimem.st, or W posted stores); the pre-norm sum can
+// be broadcast the same way as the next layer's residual.  The row lives in
+// registers between the reduction and the normalisation, so the all-reduced
+// activations never make an extra trip through HBM, and the unfused sequence
+// (all-reduce kernel, then an elementwise kernel, then a norm kernel) collapses
+// into one launch with one entry and one exit barrier.
+#include "common.cuh"
+
+namespace tccl {
+
+template <typename T, bool kNvls>
+struct AllReduceRmsNorm {
+  using Args = tccl_arn_args;
+  static constexpr int kMaxThreads = 512, kMinBlocks = 1;
+  static constexpr int kMaxVec = 4;  // 16-byte vectors per thread: hidden <= 512 * 4 * (16 / sizeof(T))
+  static constexpr int VPT = 16 / (int)sizeof(T);
+
+  static __device__ __forceinline__ void unpack(const Vec16& v, float* f) {
+    Acc<T> a;
+    a.zero();
+    a.add(v);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) f[i] = a.a[i];
+  }
+  static __device__ __forceinline__ Vec16 pack(const float* f) {
+    Acc<T> a;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) a.a[i] = f[i];
+    return a.pack();
+  }
+
+  static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
+    __shared__ float s_part[16];
+    __shared__ float s_scale;
+    const uint64_t deadline = globaltimer() + c.timeout_ns;
+    const bool nvls_bar = (a.flags & TCCL_F_NVLS_BARRIER) != 0;
+    barrier_any(c, bid, deadline, nvls_bar);
+    const int W = c.world, me = c.rank;
+    const int H = a.hidden, nvec = H / VPT;
+    const int per = (a.tokens + W - 1) / W;
+    const int row_lo = min(per * me, a.tokens), row_hi = min(row_lo + per, a.tokens);
+    const int t = threadIdx.x, nt = blockDim.x;
+    const int warp = t >> 5, lane = t & 31, nwarps = nt >> 5;
+    for (int row = row_lo + bid; row < row_hi; row += nb) {
+      const size_t rbase = (size_t)row * H * sizeof(T);
+      float v[kMaxVec][VPT];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < kMaxVec; ++j) {
+        const int i = t + j * nt;
+        if (i < nvec) {
+          const size_t off = rbase + (size_t)i * 16;
+          if (kNvls) {
+            unpack(MultimemOps<T>::ld_reduce(reinterpret_cast<const char*>(a.mc_x) + off), v[j]);
+          } else {
+            Acc<T> acc;
+            acc.zero();
+            for (int p = 0; p < W; ++p) acc.add(ld_peer(reinterpret_cast<const char*>(a.x[p]) + off));
+#pragma unroll
+            for (int e = 0; e < VPT; ++e) v[j][e] = acc.a[e];
+          }
+          float b[VPT], r[VPT];
+          if (a.bias) {
+            unpack(ld_peer(reinterpret_cast<const char*>(a.bias) + (size_t)i * 16), b);
+#pragma unroll
+            for (int e = 0; e < VPT; ++e) v[j][e] += b[e];
+          }
+          if (a.residual) {
+            unpack(ld_peer(reinterpret_cast<const char*>(a.residual) + off), r);
+#pragma unroll
+            for (int e = 0; e < VPT; ++e) v[j][e] += r[e];
+          }
+          if (a.res_out[0]) {
+            // the next layer's residual is the sum rounded to T; normalise what was stored
+            const Vec16 pk = pack(v[j]);
+            if (kNvls) {
+              multimem_st(reinterpret_cast<char*>(a.mc_res_out) + off, pk);
+            } else {
+              for (int p = 0; p < W; ++p) st_peer(reinterpret_cast<char*>(a.res_out[p]) + off, pk);
+            }
+            unpack(pk, v[j]);
+          }
+#pragma unroll
+          for (int e = 0; e < VPT; ++e) ss += v[j][e] * v[j][e];
+        }
+      }
+      // sum of squares over the row: warp shuffle, then across warps through shared memory
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) s_part[warp] = ss;
+      __syncthreads();
+      if (warp == 0) {
+        float tot = lane < nwarps ? s_part[lane] : 0.f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+        if (lane == 0) s_scale = rsqrtf(tot / (float)H + a.eps);
+      }
+      __syncthreads();
+      const float scale = s_scale;
+#pragma unroll
+      for (int j = 0; j < kMaxVec; ++j) {
+        const int i = t + j * nt;
+        if (i < nvec) {
+          float wv[VPT], o[VPT];
+          unpack(ld_peer(reinterpret_cast<const char*>(a.weight) + (size_t)i * 16), wv);
+#pragma unroll
+          for (int e = 0; e < VPT; ++e) o[e] = v[j][e] * scale * wv[e];
+          const Vec16 pk = pack(o);
+          const size_t off = rbase + (size_t)i * 16;
+          if (kNvls) {
+            multimem_st(reinterpret_cast<char*>(a.mc_out) + off, pk);
+          } else {
+            for (int p = 0; p < W; ++p) st_peer(reinterpret_cast<char*>(a.out[p]) + off, pk);
+          }
+        }
+      }
+      __syncthreads();  // s_part / s_scale are reused by the next row
+    }
+    barrier_any(c, bid, deadline, nvls_bar);  // every rank's rows have landed everywhere
+  }
+};
+
+}  // namespace tccl
+
+using namespace tccl;
+
+extern "C" int tccl_allreduce_bias_residual_rmsnorm(const tccl_comm* comm, const tccl_arn_args* args, int nvls,
+                                                    const tccl_launch* l) {
+  const int dtype = l->n_emu ? (l->meta & 0xff) : args->dtype;
+  if (nvls) {
+    switch (dtype) {
+      case TCCL_BF16: return launch_op<AllReduceRmsNorm<__nv_bfloat16, true>>(comm, args, l);
+      case TCCL_F16: return launch_op<AllReduceRmsNorm<__half, true>>(comm, args, l);
+      case TCCL_F32: return launch_op<AllReduceRmsNorm<float, true>>(comm, args, l);
+      default: return -TCCL_EDTYPE;
+    }
+  }
+  switch (dtype) {
+    case TCCL_BF16: return launch_op<AllReduceRmsNorm<__nv_bfloat16, false>>(comm, args, l);
+    case TCCL_F16: return launch_op<AllReduceRmsNorm<__half, false>>(comm, args, l);
+    case TCCL_F32: return launch_op<AllReduceRmsNorm<float, false>>(comm, args, l);
+    default: return -TCCL_EDTYPE;
+  }
+}

@@ -157,6 +157,24 @@ typedef struct tccl_tree_args {
 } tccl_tree_args;
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
 
+/* ---- fused all-reduce + bias + residual + RMSNorm ------------------------- */
+typedef struct tccl_arn_args {
+  const void* x[TCCL_MAX_WORLD];   /* every rank's partial [tokens, hidden] (symmetric, peer-mapped) */
+  void* mc_x;                      /* multicast alias of x, or NULL */
+  void* out[TCCL_MAX_WORLD];       /* every rank's normalised output (symmetric) */
+  void* mc_out;
+  void* res_out[TCCL_MAX_WORLD];   /* every rank's pre-norm sum (symmetric), or all NULL to skip it */
+  void* mc_res_out;
+  const void* bias;                /* [hidden] or NULL */
+  const void* residual;            /* local [tokens, hidden] or NULL */
+  const void* weight;              /* [hidden] */
+  float eps;
+  int32_t tokens, hidden;          /* hidden * sizeof(T) % 16 == 0, hidden <= 2048 * (16 / sizeof(T)) */
+  int32_t dtype;
+  int32_t flags;                   /* TCCL_F_NVLS_BARRIER */
+} tccl_arn_args;
+int tccl_allreduce_bias_residual_rmsnorm(const tccl_comm*, const tccl_arn_args*, int nvls, const tccl_launch*);
+
 /* ---- tcgen05 GEMM (bf16 in, fp32 accumulate in tensor memory, bf16 out) ---- */
 typedef struct tccl_gemm_args {
   const void* a;   /* [m, k], k contiguous, lda elements between rows */

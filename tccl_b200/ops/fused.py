@@ -14,9 +14,9 @@ import torch
 
 from ..parallel.world import WorldBase
 from ..utils import lib as L
-from ._common import K, get_world
+from ._common import K, check_sym_tensor, dtype_code, get_world
 
-__all__ = ["gemm_reduce_scatter", "all_gather_gemm"]
+__all__ = ["gemm_reduce_scatter", "all_gather_gemm", "all_reduce_bias_residual_rmsnorm"]
 
 
 def _locals(w: WorldBase, x):
@@ -166,3 +166,86 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, w
     w.launches += 1
     res = out if out is not None else ([outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]])
     return res, a_full
+
+
+def all_reduce_bias_residual_rmsnorm(x, weight, bias=None, residual=None, eps: float = 1e-5, out=None,
+                                     residual_out=None, *, algo: str = "auto", world: Optional[WorldBase] = None):
+    """``y = RMSNorm(all_reduce(x) + bias + residual) * weight`` in one kernel.
+
+    ``x``: this rank's partial ``[tokens, hidden]`` in symmetric memory (the output
+    of a row-parallel linear before its reduction).  ``bias`` / ``weight``:
+    ``[hidden]``; ``residual``: this rank's (replicated) ``[tokens, hidden]``.
+    ``out`` (and ``residual_out``, the pre-norm sum that becomes the next residual)
+    live in symmetric memory because every rank writes its rows into all of them;
+    they are allocated and cached per shape when omitted (pass ``residual_out=True``
+    to ask for the pre-norm sum).  Returns ``y`` or ``(y, residual_out)``."""
+    w = get_world(world)
+    check_sym_tensor(w, x, "input")
+    x0 = w.local(x, w.local_ranks[0])
+    if x0.dim() != 2:
+        raise ValueError("x must be [tokens, hidden]")
+    T, H = x0.shape
+    dt = dtype_code(x0.dtype)
+    vpt = 16 // x0.element_size()
+    if H % vpt or H > 512 * 4 * vpt:
+        raise ValueError(f"hidden must be a multiple of {vpt} and at most {512 * 4 * vpt}")
+    cache = w.__dict__.setdefault("_arn_buffers", {})
+
+    def sym(tag, given):
+        if given is not None and given is not True:
+            check_sym_tensor(w, given, tag)
+            return given
+        key = (tag, T, H, x0.dtype)
+        if key not in cache:
+            cache[key] = w.empty((T, H), x0.dtype)
+        return cache[key]
+
+    out = sym("out", out)
+    want_res = residual_out is not None and residual_out is not False
+    res_out = sym("residual_out", residual_out) if want_res else None
+    if algo == "auto":
+        algo = "nvls" if w.has_nvls and w.world_size > 2 else "p2p"
+    if algo == "nvls" and not w.has_nvls:
+        raise RuntimeError("nvls variant needs NVLS multicast")
+    Ws, Bs, Rs = _locals(w, weight), (_locals(w, bias) if bias is not None else None), \
+        (_locals(w, residual) if residual is not None else None)
+    xp, op = w.peer_ptrs(x), w.peer_ptrs(out)
+    rp = w.peer_ptrs(res_out) if want_res else None
+    args = {}
+    for r in w.local_ranks:
+        a = L.ArnArgs()
+        for q in range(w.world_size):
+            a.x[q], a.out[q] = xp[q], op[q]
+            a.res_out[q] = rp[q] if rp else 0
+        a.mc_x, a.mc_out = w.mc_ptr(x), w.mc_ptr(out)
+        a.mc_res_out = w.mc_ptr(res_out) if want_res else 0
+        for name, src in (("weight", Ws), ("bias", Bs), ("residual", Rs)):
+            if src is None:
+                setattr(a, name, 0)
+                continue
+            tns = src[r]
+            if tns.dtype != x0.dtype or not tns.is_contiguous() or tns.data_ptr() % 16:
+                raise ValueError(f"{name} must be contiguous, 16-byte aligned and of x's dtype")
+            if tns.numel() != (T * H if name == "residual" else H):
+                raise ValueError(f"{name} has the wrong size")
+            setattr(a, name, tns.data_ptr())
+        a.eps, a.tokens, a.hidden, a.dtype = float(eps), T, H, dt
+        a.flags = w.coll_flags()
+        args[r] = a
+    rows = -(-T // w.world_size)
+    grid = max(1, min(rows, w.max_ctas()))
+    fn = L.lib().tccl_allreduce_bias_residual_rmsnorm
+    nvls = 1 if algo == "nvls" else 0
+    stream = torch.cuda.current_stream(x0.device).cuda_stream
+    if w.plans is not None:
+        l = L.Launch(grid, 512, 0, dt, C.c_void_p(stream))
+        rc = fn(C.byref(w.comm), C.byref(args[w.local_ranks[0]]), nvls, C.byref(l))
+    else:
+        arr = (L.ArnArgs * w.world_size)(*[args[r] for r in w.local_ranks])
+        dev = w._to_device(arr)
+        w._keep.append(dev)
+        l = L.Launch(grid, 512, w.world_size, dt, C.c_void_p(stream))
+        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), C.c_void_p(dev.data_ptr()), nvls, C.byref(l))
+    L.check(rc, "tccl_allreduce_bias_residual_rmsnorm")
+    w.launches += 1
+    return (out, res_out) if want_res else out

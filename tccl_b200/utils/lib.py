@@ -124,6 +124,17 @@ class AgGemmArgs(C.Structure):
     ]
 
 
+class ArnArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_uint64 * MAX_WORLD), ("mc_x", C.c_uint64),
+        ("out", C.c_uint64 * MAX_WORLD), ("mc_out", C.c_uint64),
+        ("res_out", C.c_uint64 * MAX_WORLD), ("mc_res_out", C.c_uint64),
+        ("bias", C.c_uint64), ("residual", C.c_uint64), ("weight", C.c_uint64),
+        ("eps", C.c_float), ("tokens", C.c_int32), ("hidden", C.c_int32),
+        ("dtype", C.c_int32), ("flags", C.c_int32),
+    ]
+
+
 class Launch(C.Structure):
     _fields_ = [
         ("grid", C.c_int32),

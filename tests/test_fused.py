@@ -54,3 +54,30 @@ def test_all_gather_gemm(emu_worlds, W, M, N, K):
             bound = ref.abs() * 2 ** -8 + 1e-3 * (K ** 0.5) * 0.02
             assert bool((err <= bound).all()), f"rank {r}: max err {err.max().item()} ratio {(err / bound).max().item()}"
             assert torch.equal(a_full[r].float(), a_all)  # the gathered activations are left behind, exactly
+
+
+@pytest.mark.parametrize("W", [1, 2, 4, 8])
+@pytest.mark.parametrize("T,H", [(8, 256), (67, 1024), (512, 4096), (33, 8192)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_all_reduce_bias_residual_rmsnorm(emu_worlds, W, T, H, with_res):
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    x = w.from_parts([_rand((T, H), 4000 + r) for r in range(W)])
+    bias, res, weight = _rand((H,), 1, 0.5), _rand((T, H), 2), _rand((H,), 3)
+    rep = lambda t: [t for _ in range(W)]
+    got = tccl.all_reduce_bias_residual_rmsnorm(x, rep(weight), rep(bias), rep(res), eps=1e-5,
+                                                residual_out=True if with_res else None, world=w)
+    torch.cuda.synchronize()
+    w.check()
+    y, h_out = got if with_res else (got, None)
+    h = torch.stack([p.float() for p in x.parts]).sum(0) + bias.float() + res.float()
+    if with_res:
+        for r in range(W):
+            assert bool(((h_out[r].float() - h).abs() <= h.abs() * 2 ** -8 + 1e-5).all())
+        h = h.to(torch.bfloat16).float()  # the kernel normalises the rounded sum it stored
+    ref = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + 1e-5) * weight.float()
+    for r in range(W):
+        err = (y[r].float() - ref).abs()
+        assert bool((err <= ref.abs() * 2 ** -7 + 1e-3).all()), f"max err {err.max().item()}"
+        assert torch.equal(y[r], y[0])
