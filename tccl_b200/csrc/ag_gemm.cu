@@ -30,6 +30,7 @@ struct alignas(64) AgGemmParams {
   __nv_bfloat16* out;
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank, comm_ctas;
+  int swiglu;  // 1: columns [0,128) of every 256-wide tile are gate, [128,256) up; out = silu(gate) * up
 };
 
 struct AgGemmPolicy {
@@ -81,6 +82,33 @@ struct AgGemmPolicy {
   __device__ __forceinline__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort&) const {
     const int row = mt * BM + quad * 32 + lane;
     __nv_bfloat16* crow = p->out + (size_t)row * p->ldo;
+    if (p->swiglu) {
+      // SwiGLU fused into the epilogue: the weight rows are packed so that each 256-wide
+      // tile holds 128 gate columns followed by the 128 matching up columns
+#pragma unroll 1
+      for (int cg = 0; cg < BN / 64; ++cg) {
+        uint32_t g[32], u[32];
+        tmem_ld_32x32(taddr + cg * 32, g);
+        tmem_ld_32x32(taddr + BN / 2 + cg * 32, u);
+        tmem_ld_wait();
+        const int col0 = nt * (BN / 2) + cg * 32;
+        if (row < p->shp.M) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 < p->shp.N / 2) {
+              uint32_t o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float gv = __uint_as_float(g[v * 8 + e]), uv = __uint_as_float(u[v * 8 + e]);
+                o[e] = __float_as_uint(gv / (1.f + __expf(-gv)) * uv);
+              }
+              st_local(crow + col0 + v * 8, pack8_bf16(o));
+            }
+          }
+        }
+      }
+      return true;
+    }
 #pragma unroll 1
     for (int cg = 0; cg < BN / 32; ++cg) {
       uint32_t r[32];
@@ -199,6 +227,8 @@ static int fill_params(AgGemmParams* p, const tccl_ag_gemm_args* g, int world, i
   p->tiles_n = (g->n + BN - 1) / BN;
   p->tiles_m_per_rank = rows / BM;
   p->comm_ctas = g->comm_ctas;
+  p->swiglu = g->swiglu;
+  if (g->swiglu && (g->n % BN)) return -TCCL_ESIZE;  // whole gate|up tiles only
   if (p->tiles_m_per_rank > TCCL_MAX_ROW_TILES) return -TCCL_ESIZE;
   return 0;
 }

@@ -214,6 +214,8 @@ typedef struct tccl_ag_gemm_args {
   int32_t m, n, k;                  /* m % (world * 128) == 0, n % 8 == 0, k % 8 == 0 */
   int32_t lda_shard, lda_full, ldb, ldo;
   int32_t comm_ctas;                /* CTAs that move the shard; the others run the GEMM */
+  int32_t swiglu;                   /* 1: every 256-row block of bt is 128 gate rows then the 128 matching up
+                                       rows; out is [m, n / 2] = silu(gate) * up (n % 256 == 0) */
 } tccl_ag_gemm_args;
 uint64_t tccl_ag_gemm_param_bytes(void);
 /* same calling convention as tccl_gemm_reduce_scatter */

@@ -1,0 +1,1 @@
+from .tp_mlp import TensorParallelMLP

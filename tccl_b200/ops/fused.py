@@ -16,7 +16,7 @@ from ..parallel.world import WorldBase
 from ..utils import lib as L
 from ._common import K, check_sym_tensor, dtype_code, get_world
 
-__all__ = ["gemm_reduce_scatter", "all_gather_gemm", "all_reduce_bias_residual_rmsnorm"]
+__all__ = ["gemm_reduce_scatter", "all_gather_gemm", "all_reduce_bias_residual_rmsnorm", "pack_gate_up"]
 
 
 def _locals(w: WorldBase, x):
@@ -94,7 +94,8 @@ def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
     return [outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]]
 
 
-def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, world: Optional[WorldBase] = None):
+def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, swiglu: bool = False,
+                    world: Optional[WorldBase] = None):
     """``out_r = all_gather(a_shard) @ bt_r.T`` — tensor-parallel up-projection
     fused with the all-gather of the token rows.
 
@@ -102,7 +103,11 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, w
     its ``[N_r, K]`` weight slice.  ``a_full`` is the ``[M, K]`` gathered buffer in
     symmetric memory (allocated and cached per shape when omitted); it holds the
     gathered activations afterwards.  Returns ``(out, a_full)`` with ``out`` the
-    rank's ``[M, N_r]`` result.  ``M % (128 W) == 0``."""
+    rank's ``[M, N_r]`` result.  ``M % (128 W) == 0``.
+
+    ``swiglu=True`` fuses the gated activation into the epilogue: ``bt`` must be
+    packed by :func:`pack_gate_up` (every 256-row block = 128 gate rows, then the
+    128 matching up rows) and ``out`` is ``[M, N_r / 2] = silu(gate) * up``."""
     w = get_world(world)
     W = w.world_size
     As, Bs = _locals(w, a_shard), _locals(w, bt)
@@ -115,6 +120,9 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, w
         raise ValueError("a_shard is [M / W, K], bt is [N, K]")
     if rows % 128 or N % 8 or Kd % 8:
         raise ValueError(f"need (M / W) % 128 == 0, N % 8 == 0, K % 8 == 0 (got M/W={rows}, N={N}, K={Kd})")
+    if swiglu and N % 256:
+        raise ValueError("swiglu needs N % 256 == 0 (whole gate|up tiles)")
+    n_out = N // 2 if swiglu else N
     if a_full is None:
         cache = w.__dict__.setdefault("_ag_buffers", {})
         a_full = cache.get((M, Kd))
@@ -138,7 +146,9 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, w
         ar, br = As[r], Bs[r]
         if ar.stride(1) != 1 or br.stride(1) != 1:
             raise ValueError("operands must have a unit inner stride")
-        o = Os[r] if Os is not None else torch.empty((M, N), dtype=torch.bfloat16, device=ar.device)
+        o = Os[r] if Os is not None else torch.empty((M, n_out), dtype=torch.bfloat16, device=ar.device)
+        if o.shape != (M, n_out) or o.dtype != torch.bfloat16 or o.stride(1) != 1:
+            raise ValueError(f"out must be bf16 [{M}, {n_out}] with a unit inner stride")
         outs[r] = o
         g = L.AgGemmArgs()
         g.a_shard = ar.data_ptr()
@@ -149,6 +159,7 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, w
         g.m, g.n, g.k = M, N, Kd
         g.lda_shard, g.lda_full, g.ldb, g.ldo = ar.stride(0), Kd, br.stride(0), o.stride(0)
         g.comm_ctas = comm_ctas
+        g.swiglu = 1 if swiglu else 0
         arr[i] = g
     stream = torch.cuda.current_stream(a0.device).cuda_stream
     fn = lib.tccl_allgather_gemm
@@ -249,3 +260,15 @@ def all_reduce_bias_residual_rmsnorm(x, weight, bias=None, residual=None, eps: f
     L.check(rc, "tccl_allreduce_bias_residual_rmsnorm")
     w.launches += 1
     return (out, res_out) if want_res else out
+
+
+def pack_gate_up(gate_w: torch.Tensor, up_w: torch.Tensor) -> torch.Tensor:
+    """Interleave ``gate_w`` and ``up_w`` (both ``[F, K]``, ``F % 128 == 0``) in
+    blocks of 128 rows — gate rows ``[128 j, 128 j + 128)`` followed by the same
+    rows of ``up_w`` — which is the weight layout the ``swiglu`` epilogue of
+    :func:`all_gather_gemm` expects (one 256-wide output tile = 128 gate columns
+    and the 128 up columns they multiply)."""
+    F, Kd = gate_w.shape
+    if up_w.shape != gate_w.shape or F % 128:
+        raise ValueError("gate and up weights must both be [F, K] with F % 128 == 0")
+    return torch.stack([gate_w.view(F // 128, 128, Kd), up_w.view(F // 128, 128, Kd)], dim=1).reshape(2 * F, Kd).contiguous()
