@@ -138,14 +138,29 @@ __device__ void ag_comm_part(const tccl_comm& c, const AgGemmParams& p, int bid,
     const uint32_t nvec = (uint32_t)BM * vec_per_row;
     const uint32_t per = (nvec + nc - 1) / nc;
     const uint32_t lo = min(per * bid, nvec), hi = min(lo + per, nvec);
-    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-      const int row = rt * BM + i / vec_per_row, col = (i % vec_per_row) * 8;
-      const Vec16 v = ld_peer(p.a_shard + ((size_t)row * p.lda_shard + col) * 2);
-      const size_t dst = ((size_t)(me * rows_per_rank + row) * p.lda_full + col) * 2;
-      if (p.mc_a_full) {
-        multimem_st(p.mc_a_full + dst, v);
-      } else {
-        for (int q = 0; q < W; ++q) st_peer(p.a_full[q] + dst, v);
+    // 8 vectors per thread in flight: a mover CTA has to keep ~32 KB on the wire to matter
+    constexpr int U = 8;
+    for (uint32_t i0 = lo + threadIdx.x; i0 < hi; i0 += U * blockDim.x) {
+      Vec16 v[U];
+      size_t dst[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t i = i0 + u * blockDim.x;
+        if (i < hi) {
+          const int row = rt * BM + i / vec_per_row, col = (i % vec_per_row) * 8;
+          v[u] = ld_peer(p.a_shard + ((size_t)row * p.lda_shard + col) * 2);
+          dst[u] = ((size_t)(me * rows_per_rank + row) * p.lda_full + col) * 2;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * blockDim.x < hi) {
+          if (p.mc_a_full) {
+            multimem_st(p.mc_a_full + dst[u], v[u]);
+          } else {
+            for (int q = 0; q < W; ++q) st_peer(p.a_full[q] + dst[u], v[u]);
+          }
+        }
       }
     }
     __syncthreads();  // this CTA's share of the row tile is stored

@@ -13,11 +13,14 @@
 
 namespace tccl {
 
-template <typename T, bool kNvls>
+template <typename T, bool kNvls, int MV>
 struct AllReduceRmsNorm {
   using Args = tccl_arn_args;
-  static constexpr int kMaxThreads = 512, kMinBlocks = 1;
-  static constexpr int kMaxVec = 4;  // 16-byte vectors per thread: hidden <= 512 * 4 * (16 / sizeof(T))
+  // MV = 16-byte vectors per thread (hidden <= 512 * MV * (16 / sizeof(T))).  With one
+  // vector per thread the kernel is small enough for two CTAs per SM: twice the rows in
+  // flight, which is what hides the peer-load and barrier latency of a row.
+  static constexpr int kMaxThreads = 512, kMinBlocks = MV == 1 ? 2 : 1;
+  static constexpr int kMaxVec = MV;
   static constexpr int VPT = 16 / (int)sizeof(T);
 
   static __device__ __forceinline__ void unpack(const Vec16& v, float* f) {
@@ -129,21 +132,31 @@ struct AllReduceRmsNorm {
 
 using namespace tccl;
 
+template <typename T, bool kNvls>
+static int launch_by_width(const tccl_comm* comm, const tccl_arn_args* args, const tccl_launch* l, int hidden) {
+  const int nvec = hidden / (16 / (int)sizeof(T));
+  if (nvec <= 512) return launch_op<AllReduceRmsNorm<T, kNvls, 1>>(comm, args, l);
+  if (nvec <= 1024) return launch_op<AllReduceRmsNorm<T, kNvls, 2>>(comm, args, l);
+  if (nvec <= 2048) return launch_op<AllReduceRmsNorm<T, kNvls, 4>>(comm, args, l);
+  return -TCCL_ESIZE;
+}
+
+// `hidden` is passed separately because in emulated mode `args` is a device pointer.
 extern "C" int tccl_allreduce_bias_residual_rmsnorm(const tccl_comm* comm, const tccl_arn_args* args, int nvls,
-                                                    const tccl_launch* l) {
+                                                    int hidden, const tccl_launch* l) {
   const int dtype = l->n_emu ? (l->meta & 0xff) : args->dtype;
   if (nvls) {
     switch (dtype) {
-      case TCCL_BF16: return launch_op<AllReduceRmsNorm<__nv_bfloat16, true>>(comm, args, l);
-      case TCCL_F16: return launch_op<AllReduceRmsNorm<__half, true>>(comm, args, l);
-      case TCCL_F32: return launch_op<AllReduceRmsNorm<float, true>>(comm, args, l);
+      case TCCL_BF16: return launch_by_width<__nv_bfloat16, true>(comm, args, l, hidden);
+      case TCCL_F16: return launch_by_width<__half, true>(comm, args, l, hidden);
+      case TCCL_F32: return launch_by_width<float, true>(comm, args, l, hidden);
       default: return -TCCL_EDTYPE;
     }
   }
   switch (dtype) {
-    case TCCL_BF16: return launch_op<AllReduceRmsNorm<__nv_bfloat16, false>>(comm, args, l);
-    case TCCL_F16: return launch_op<AllReduceRmsNorm<__half, false>>(comm, args, l);
-    case TCCL_F32: return launch_op<AllReduceRmsNorm<float, false>>(comm, args, l);
+    case TCCL_BF16: return launch_by_width<__nv_bfloat16, false>(comm, args, l, hidden);
+    case TCCL_F16: return launch_by_width<__half, false>(comm, args, l, hidden);
+    case TCCL_F32: return launch_by_width<float, false>(comm, args, l, hidden);
     default: return -TCCL_EDTYPE;
   }
 }

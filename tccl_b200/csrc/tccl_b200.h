@@ -173,7 +173,9 @@ typedef struct tccl_arn_args {
   int32_t dtype;
   int32_t flags;                   /* TCCL_F_NVLS_BARRIER */
 } tccl_arn_args;
-int tccl_allreduce_bias_residual_rmsnorm(const tccl_comm*, const tccl_arn_args*, int nvls, const tccl_launch*);
+/* `hidden` repeats args->hidden for the host (in emulated mode `args` is a device pointer) */
+int tccl_allreduce_bias_residual_rmsnorm(const tccl_comm*, const tccl_arn_args*, int nvls, int hidden,
+                                         const tccl_launch*);
 
 /* ---- tcgen05 GEMM (bf16 in, fp32 accumulate in tensor memory, bf16 out) ---- */
 typedef struct tccl_gemm_args {

@@ -244,19 +244,20 @@ def all_reduce_bias_residual_rmsnorm(x, weight, bias=None, residual=None, eps: f
         a.flags = w.coll_flags()
         args[r] = a
     rows = -(-T // w.world_size)
-    grid = max(1, min(rows, w.max_ctas()))
+    per_sm = 2 if (H // vpt) <= 512 and w.plans is not None else 1  # narrow rows: two CTAs per SM
+    grid = max(1, min(rows, w.max_ctas() * per_sm, K["TCCL_MAX_BLOCKS"]))
     fn = L.lib().tccl_allreduce_bias_residual_rmsnorm
     nvls = 1 if algo == "nvls" else 0
     stream = torch.cuda.current_stream(x0.device).cuda_stream
     if w.plans is not None:
         l = L.Launch(grid, 512, 0, dt, C.c_void_p(stream))
-        rc = fn(C.byref(w.comm), C.byref(args[w.local_ranks[0]]), nvls, C.byref(l))
+        rc = fn(C.byref(w.comm), C.byref(args[w.local_ranks[0]]), nvls, H, C.byref(l))
     else:
         arr = (L.ArnArgs * w.world_size)(*[args[r] for r in w.local_ranks])
         dev = w._to_device(arr)
         w._keep.append(dev)
         l = L.Launch(grid, 512, w.world_size, dt, C.c_void_p(stream))
-        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), C.c_void_p(dev.data_ptr()), nvls, C.byref(l))
+        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), C.c_void_p(dev.data_ptr()), nvls, H, C.byref(l))
     L.check(rc, "tccl_allreduce_bias_residual_rmsnorm")
     w.launches += 1
     return (out, res_out) if want_res else out
