@@ -42,6 +42,7 @@ def main():
     ap.add_argument("--gemm-tflops", type=float, default=1391.6, help="measured sustained cuBLAS bf16 peak")
     ap.add_argument("--link-gbs", type=float, default=770.0)
     ap.add_argument("--flush-l2", type=int, default=1)
+    ap.add_argument("--ag-comm-ctas", default="0", help="comma list of data-mover CTA counts to try for (b); 0 = auto")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -117,8 +118,9 @@ def main():
     flops = 2.0 * T * H * Il
     link = (W - 1) * rows * H * 2
     o2 = torch.empty(T, Il, dtype=torch.bfloat16, device="cuda")
-    report("all_gather_gemm", "tccl_b200 fused", timeit(lambda: tccl.all_gather_gemm(x_sh, wu_r, out=o2)), flops, link,
-           ok_b)
+    for cc in [int(v) for v in a.ag_comm_ctas.split(",")]:
+        report("all_gather_gemm", f"tccl_b200 fused (movers={cc or 'auto'})",
+               timeit(lambda: tccl.all_gather_gemm(x_sh, wu_r, out=o2, comm_ctas=cc)), flops, link, ok_b)
     gathered = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
 
     def unfused_b():

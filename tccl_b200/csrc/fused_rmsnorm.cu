@@ -21,6 +21,10 @@ struct AllReduceRmsNorm {
   // flight, which is what hides the peer-load and barrier latency of a row.
   static constexpr int kMaxThreads = 512, kMinBlocks = MV == 1 ? 2 : 1;
   static constexpr int kMaxVec = MV;
+  // rows handled together by a CTA: all their loads are issued before the first
+  // reduction, so a CTA pays the peer-load / switch latency once per R rows
+  // (measured on 8xB200, 4096 x 4096 bf16: R = 1 with two CTAs per SM beats R = 4 with fewer CTAs)
+  static constexpr int R = 1;
   static constexpr int VPT = 16 / (int)sizeof(T);
 
   static __device__ __forceinline__ void unpack(const Vec16& v, float* f) {
@@ -38,8 +42,8 @@ struct AllReduceRmsNorm {
   }
 
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
-    __shared__ float s_part[16];
-    __shared__ float s_scale;
+    __shared__ float s_part[R][16];
+    __shared__ float s_scale[R];
     const uint64_t deadline = globaltimer() + c.timeout_ns;
     const bool nvls_bar = (a.flags & TCCL_F_NVLS_BARRIER) != 0;
     barrier_any(c, bid, deadline, nvls_bar);
@@ -49,80 +53,111 @@ struct AllReduceRmsNorm {
     const int row_lo = min(per * me, a.tokens), row_hi = min(row_lo + per, a.tokens);
     const int t = threadIdx.x, nt = blockDim.x;
     const int warp = t >> 5, lane = t & 31, nwarps = nt >> 5;
-    for (int row = row_lo + bid; row < row_hi; row += nb) {
-      const size_t rbase = (size_t)row * H * sizeof(T);
-      float v[kMaxVec][VPT];
-      float ss = 0.f;
+    for (int row0 = row_lo + bid * R; row0 < row_hi; row0 += nb * R) {
+      float v[R][kMaxVec][VPT];
+      float ss[R];
+      // phase 1: fetch and sum the partial rows (all R rows in flight at once)
 #pragma unroll
-      for (int j = 0; j < kMaxVec; ++j) {
-        const int i = t + j * nt;
-        if (i < nvec) {
-          const size_t off = rbase + (size_t)i * 16;
-          if (kNvls) {
-            unpack(MultimemOps<T>::ld_reduce(reinterpret_cast<const char*>(a.mc_x) + off), v[j]);
-          } else {
-            Acc<T> acc;
-            acc.zero();
-            for (int p = 0; p < W; ++p) acc.add(ld_peer(reinterpret_cast<const char*>(a.x[p]) + off));
+      for (int q = 0; q < R; ++q) {
+        const int row = row0 + q;
+        ss[q] = 0.f;
+        if (row < row_hi) {
+          const size_t rbase = (size_t)row * H * sizeof(T);
 #pragma unroll
-            for (int e = 0; e < VPT; ++e) v[j][e] = acc.a[e];
-          }
-          float b[VPT], r[VPT];
-          if (a.bias) {
-            unpack(ld_peer(reinterpret_cast<const char*>(a.bias) + (size_t)i * 16), b);
+          for (int j = 0; j < kMaxVec; ++j) {
+            const int i = t + j * nt;
+            if (i < nvec) {
+              const size_t off = rbase + (size_t)i * 16;
+              if (kNvls) {
+                unpack(MultimemOps<T>::ld_reduce(reinterpret_cast<const char*>(a.mc_x) + off), v[q][j]);
+              } else {
+                Acc<T> acc;
+                acc.zero();
+                for (int p = 0; p < W; ++p) acc.add(ld_peer(reinterpret_cast<const char*>(a.x[p]) + off));
 #pragma unroll
-            for (int e = 0; e < VPT; ++e) v[j][e] += b[e];
-          }
-          if (a.residual) {
-            unpack(ld_peer(reinterpret_cast<const char*>(a.residual) + off), r);
-#pragma unroll
-            for (int e = 0; e < VPT; ++e) v[j][e] += r[e];
-          }
-          if (a.res_out[0]) {
-            // the next layer's residual is the sum rounded to T; normalise what was stored
-            const Vec16 pk = pack(v[j]);
-            if (kNvls) {
-              multimem_st(reinterpret_cast<char*>(a.mc_res_out) + off, pk);
-            } else {
-              for (int p = 0; p < W; ++p) st_peer(reinterpret_cast<char*>(a.res_out[p]) + off, pk);
+                for (int e = 0; e < VPT; ++e) v[q][j][e] = acc.a[e];
+              }
             }
-            unpack(pk, v[j]);
           }
-#pragma unroll
-          for (int e = 0; e < VPT; ++e) ss += v[j][e] * v[j][e];
         }
       }
-      // sum of squares over the row: warp shuffle, then across warps through shared memory
+      // phase 2: bias, residual, optional pre-norm output, sum of squares
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      if (lane == 0) s_part[warp] = ss;
+      for (int q = 0; q < R; ++q) {
+        const int row = row0 + q;
+        if (row < row_hi) {
+          const size_t rbase = (size_t)row * H * sizeof(T);
+#pragma unroll
+          for (int j = 0; j < kMaxVec; ++j) {
+            const int i = t + j * nt;
+            if (i < nvec) {
+              const size_t off = rbase + (size_t)i * 16;
+              float b[VPT], r[VPT];
+              if (a.bias) {
+                unpack(ld_peer(reinterpret_cast<const char*>(a.bias) + (size_t)i * 16), b);
+#pragma unroll
+                for (int e = 0; e < VPT; ++e) v[q][j][e] += b[e];
+              }
+              if (a.residual) {
+                unpack(ld_peer(reinterpret_cast<const char*>(a.residual) + off), r);
+#pragma unroll
+                for (int e = 0; e < VPT; ++e) v[q][j][e] += r[e];
+              }
+              if (a.res_out[0]) {
+                // the next layer's residual is the sum rounded to T; normalise what was stored
+                const Vec16 pk = pack(v[q][j]);
+                if (kNvls) {
+                  multimem_st(reinterpret_cast<char*>(a.mc_res_out) + off, pk);
+                } else {
+                  for (int p = 0; p < W; ++p) st_peer(reinterpret_cast<char*>(a.res_out[p]) + off, pk);
+                }
+                unpack(pk, v[q][j]);
+              }
+#pragma unroll
+              for (int e = 0; e < VPT; ++e) ss[q] += v[q][j][e] * v[q][j][e];
+            }
+          }
+        }
+        // sum of squares over the row: warp shuffle, then across warps through shared memory
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss[q] += __shfl_xor_sync(0xffffffffu, ss[q], o);
+        if (lane == 0) s_part[q][warp] = ss[q];
+      }
       __syncthreads();
-      if (warp == 0) {
-        float tot = lane < nwarps ? s_part[lane] : 0.f;
+      if (warp < R) {
+        float tot = lane < nwarps ? s_part[warp][lane] : 0.f;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
-        if (lane == 0) s_scale = rsqrtf(tot / (float)H + a.eps);
+        if (lane == 0) s_scale[warp] = rsqrtf(tot / (float)H + a.eps);
       }
       __syncthreads();
-      const float scale = s_scale;
+      // phase 3: normalise and store to every rank
 #pragma unroll
-      for (int j = 0; j < kMaxVec; ++j) {
-        const int i = t + j * nt;
-        if (i < nvec) {
-          float wv[VPT], o[VPT];
-          unpack(ld_peer(reinterpret_cast<const char*>(a.weight) + (size_t)i * 16), wv);
+      for (int q = 0; q < R; ++q) {
+        const int row = row0 + q;
+        if (row < row_hi) {
+          const size_t rbase = (size_t)row * H * sizeof(T);
+          const float scale = s_scale[q];
 #pragma unroll
-          for (int e = 0; e < VPT; ++e) o[e] = v[j][e] * scale * wv[e];
-          const Vec16 pk = pack(o);
-          const size_t off = rbase + (size_t)i * 16;
-          if (kNvls) {
-            multimem_st(reinterpret_cast<char*>(a.mc_out) + off, pk);
-          } else {
-            for (int p = 0; p < W; ++p) st_peer(reinterpret_cast<char*>(a.out[p]) + off, pk);
+          for (int j = 0; j < kMaxVec; ++j) {
+            const int i = t + j * nt;
+            if (i < nvec) {
+              float wv[VPT], o[VPT];
+              unpack(ld_peer(reinterpret_cast<const char*>(a.weight) + (size_t)i * 16), wv);
+#pragma unroll
+              for (int e = 0; e < VPT; ++e) o[e] = v[q][j][e] * scale * wv[e];
+              const Vec16 pk = pack(o);
+              const size_t off = rbase + (size_t)i * 16;
+              if (kNvls) {
+                multimem_st(reinterpret_cast<char*>(a.mc_out) + off, pk);
+              } else {
+                for (int p = 0; p < W; ++p) st_peer(reinterpret_cast<char*>(a.out[p]) + off, pk);
+              }
+            }
           }
         }
       }
-      __syncthreads();  // s_part / s_scale are reused by the next row
+      __syncthreads();  // s_part / s_scale are reused by the next batch of rows
     }
     barrier_any(c, bid, deadline, nvls_bar);  // every rank's rows have landed everywhere
   }

@@ -94,24 +94,37 @@ struct GemmRsPolicy {
     const int orow = (mt - owner * p->tiles_m_per_rank) * BM + row;
     __nv_bfloat16* dst = p->out + (size_t)orow * p->ldo + nt * BN;
     const bool row_ok = mt * BM + row < p->shp.M;
+    // All W-1 staged partials of a 32-column group are requested before any is
+    // consumed: 4 (W-1) 16-byte loads per thread in flight.  A reduction that waits
+    // for each load in turn leaves the epilogue latency-bound (measured: the own
+    // tiles then take as long as the whole GEMM).
 #pragma unroll 1
     for (int cg = 0; cg < BN / 32; ++cg) {
+      Vec16 x[TCCL_MAX_WORLD - 1][4];
+#pragma unroll
+      for (int j = 0; j < TCCL_MAX_WORLD - 1; ++j) {
+        if (j < W - 1) {
+          const int src = j < me ? j : j + 1;
+          const char* slot = c->stage[me] + ((size_t)src * tpo + lt) * kSlotBytes;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) x[j][v] = ld_peer(slot + slot_off(row, cg, v));
+        }
+      }
       uint32_t r[32];
       tmem_ld_32x32(taddr + cg * 32, r);
       tmem_ld_wait();
-      float acc[32];
+      float* acc = reinterpret_cast<float*>(r);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) acc[i] = __uint_as_float(r[i]);
-      for (int src = 0; src < W; ++src) {
-        if (src == me) continue;
-        const char* slot = c->stage[me] + ((size_t)src * tpo + lt) * kSlotBytes;
+      for (int j = 0; j < TCCL_MAX_WORLD - 1; ++j) {
+        if (j < W - 1) {
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const Vec16 x = ld_peer(slot + slot_off(row, cg, v));
-          acc[v * 8 + 0] += Acc<__nv_bfloat16>::lo(x.x); acc[v * 8 + 1] += Acc<__nv_bfloat16>::hi(x.x);
-          acc[v * 8 + 2] += Acc<__nv_bfloat16>::lo(x.y); acc[v * 8 + 3] += Acc<__nv_bfloat16>::hi(x.y);
-          acc[v * 8 + 4] += Acc<__nv_bfloat16>::lo(x.z); acc[v * 8 + 5] += Acc<__nv_bfloat16>::hi(x.z);
-          acc[v * 8 + 6] += Acc<__nv_bfloat16>::lo(x.w); acc[v * 8 + 7] += Acc<__nv_bfloat16>::hi(x.w);
+          for (int v = 0; v < 4; ++v) {
+            const Vec16& q = x[j][v];
+            acc[v * 8 + 0] += Acc<__nv_bfloat16>::lo(q.x); acc[v * 8 + 1] += Acc<__nv_bfloat16>::hi(q.x);
+            acc[v * 8 + 2] += Acc<__nv_bfloat16>::lo(q.y); acc[v * 8 + 3] += Acc<__nv_bfloat16>::hi(q.y);
+            acc[v * 8 + 4] += Acc<__nv_bfloat16>::lo(q.z); acc[v * 8 + 5] += Acc<__nv_bfloat16>::hi(q.z);
+            acc[v * 8 + 6] += Acc<__nv_bfloat16>::lo(q.w); acc[v * 8 + 7] += Acc<__nv_bfloat16>::hi(q.w);
+          }
         }
       }
       if (row_ok) {

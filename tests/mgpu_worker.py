@@ -121,6 +121,71 @@ def main():
                     return torch.equal(out.cpu(), ref)
                 case(f"allgather/{algo}/{n}", push)
 
+    # fused compute + collective kernels against fp32 references computed on this GPU
+    def rnd(shape, seed, scale=1.0):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+    M, N, Kr = 128 * W * 2, 512, 448
+
+    def gemm_rs():
+        a, bt = rnd((M, Kr), 4000 + rank), rnd((N, Kr), 5000 + rank, 0.02)
+        ok = True
+        for _ in range(2):
+            out = tccl.gemm_reduce_scatter(a, bt)
+            torch.cuda.synchronize()
+            rows = M // W
+            ref = sum(rnd((M, Kr), 4000 + r)[rank * rows:(rank + 1) * rows].float() @ rnd((N, Kr), 5000 + r, 0.02).float().t()
+                      for r in range(W))
+            ok = ok and bool(((out.float() - ref).abs() <= ref.abs() * 2 ** -7 + 0.02 * W).all())
+        return ok
+    case("fused/gemm_reduce_scatter", gemm_rs)
+
+    def ag_gemm():
+        rows = M // W
+        sh, bt = rnd((rows, 512), 4000 + rank), rnd((768, 512), 6000 + rank, 0.02)
+        ok = True
+        for _ in range(2):
+            out, a_full = tccl.all_gather_gemm(sh, bt)
+            torch.cuda.synchronize()
+            x_all = torch.cat([rnd((rows, 512), 4000 + r) for r in range(W)])
+            ref = x_all.float() @ bt.float().t()
+            ok = ok and bool(((out.float() - ref).abs() <= ref.abs() * 2 ** -8 + 1e-2).all()) and torch.equal(a_full, x_all)
+        return ok
+    case("fused/all_gather_gemm", ag_gemm)
+
+    for algo in ["p2p"] + (["nvls"] if nvls else []):
+        def arn(algo=algo):
+            T, H = 67 * W, 4096
+            xp = w.empty((T, H), torch.bfloat16)
+            xp.copy_(rnd((T, H), 4000 + rank))
+            bias, resid, wn = rnd((H,), 1, 0.5), rnd((T, H), 2), rnd((H,), 3)
+            y, h_out = tccl.all_reduce_bias_residual_rmsnorm(xp, wn, bias, resid, eps=1e-5, residual_out=True, algo=algo)
+            torch.cuda.synchronize()
+            h = sum(rnd((T, H), 4000 + r).float() for r in range(W)) + bias.float() + resid.float()
+            # NVLS hands the cross-rank sum back already rounded to bf16 (not to nearest), then
+            # bias and residual are added and the result is rounded again
+            tol = 2 ** -6 if algo == "nvls" else 2 ** -7
+            ok = bool(((h_out.float() - h).abs() <= h.abs() * tol + 2e-2).all())
+            hb = h_out.float()
+            ref = hb * torch.rsqrt((hb * hb).mean(-1, keepdim=True) + 1e-5) * wn.float()
+            return ok and bool(((y.float() - ref).abs() <= ref.abs() * 2 ** -7 + 1e-3).all())
+        case(f"fused/allreduce_rmsnorm/{algo}", arn)
+
+    def tree():
+        ok = True
+        for n in (4096, (1 << 20) + 64, 1 << 24):
+            xs = [seeded(n, torch.bfloat16, 2000 + r) for r in range(W)]
+            ref = torch.stack([x.float() for x in xs]).sum(0)
+            x = w.empty(n, torch.bfloat16)
+            x.copy_(xs[rank])
+            out = tccl.double_tree_all_reduce(x)
+            torch.cuda.synchronize()
+            err = (out.float().cpu() - ref).abs()
+            ok = ok and bool((err <= ref.abs() * 2 ** -8 * 4 + 0.08).all()) and torch.equal(x.cpu(), xs[rank])
+        return ok
+    case("allreduce/tree", tree)
+
     # back-to-back stress with changing data (WAR/RAW hazards)
     def stress():
         n = 4096
