@@ -128,9 +128,10 @@ struct Entry {
 template <typename T, int W>
 struct AllReduceOneShotP2P {
   using Args = tccl_coll_args;
-  static constexpr int kMaxThreads = 512, kMinBlocks = 1;
+  // one rank: the reduction is a copy; keep it lean so two CTAs fit an SM
+  static constexpr int kMaxThreads = 512, kMinBlocks = W == 1 ? 2 : 1;
   static constexpr int kMaxW = W ? W : TCCL_MAX_WORLD;
-  static constexpr int U = (W == 0 || W >= 8) ? 2 : 4;  // vectors per thread per pass
+  static constexpr int U = W == 1 ? 8 : ((W == 0 || W >= 8) ? 2 : 4);  // vectors per thread per pass
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
     Entry sync(c, a.flags, bid);
     const int world = WorldOf<W>::get(c);
@@ -149,6 +150,10 @@ struct AllReduceOneShotP2P {
 #pragma unroll
       for (int u = 0; u < U; ++u)
         if (i0 + u * bs < nvec) {
+          if (W == 1) {  // nothing to add: stream the bits through
+            st_local_cs(vptr<T>(a.out, i0 + u * bs), v[0][u]);
+            continue;
+          }
           Acc<T> acc;
           acc.zero();
 #pragma unroll
@@ -438,6 +443,7 @@ template <template <typename, int> class Op>
 static int dispatch(const tccl_comm* comm, const tccl_coll_args* args, const tccl_launch* l, int world, int dtype) {
 #define TCCL_W(T)                                                         \
   switch (world) {                                                        \
+    case 1: return launch_op<Op<T, 1>>(comm, args, l);                    \
     case 2: return launch_op<Op<T, 2>>(comm, args, l);                    \
     case 4: return launch_op<Op<T, 4>>(comm, args, l);                    \
     case 8: return launch_op<Op<T, 8>>(comm, args, l);                    \
