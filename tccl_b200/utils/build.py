@@ -20,6 +20,7 @@ CSRC = PKG / "csrc"
 BUILD = PKG / "_build"
 LIBDIR = PKG / "_lib"
 LIB = LIBDIR / "libtccl_b200.so"
+HOST_LIB = LIBDIR / "libtccl_hostproto.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -95,5 +96,28 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     return LIB
 
 
+def build_host(verbose: bool = False, force: bool = False) -> Path:
+    """Compile the host-side protocol model (csrc/host/*.cpp, plain g++, no CUDA)."""
+    LIBDIR.mkdir(exist_ok=True)
+    BUILD.mkdir(exist_ok=True)
+    srcs = sorted((CSRC / "host").glob("*.cpp"))
+    stamp = BUILD / "hostproto.sha"
+    dig = _digest(srcs + headers(), "g++ -O2 -std=c++17")
+    if force or not HOST_LIB.exists() or not stamp.exists() or stamp.read_text() != dig:
+        cxx = os.environ.get("CXX") or shutil.which("g++") or "g++"
+        tmp = HOST_LIB.with_suffix(f".tmp{os.getpid()}.so")
+        cmd = [cxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-pthread", "-I", str(CSRC), "-o", str(tmp),
+               *map(str, srcs)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"g++ failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, HOST_LIB)  # atomic: a concurrent loader never sees a half-written file
+        stamp.write_text(dig)
+        if verbose:
+            print(f"[tccl_b200.build] built {HOST_LIB}", file=sys.stderr)
+    return HOST_LIB
+
+
 if __name__ == "__main__":
+    build_host(verbose=True, force="--force" in sys.argv)
     build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)

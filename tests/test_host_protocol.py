@@ -1,0 +1,66 @@
+"""Failure handling of the synchronisation protocols, tested on the host: CPU
+processes run the C++ twin of the device protocol over shared memory, and the
+faults (a lost signal, a stalled rank, a rank that stops or never joins) are
+injected there.  Every wait is bounded, so a failed peer turns into a TIMEOUT
+status that names the peer — never into a hang."""
+import time
+
+import numpy as np
+import pytest
+
+from tccl_b200.utils.hostproto import run_ranks
+
+
+def test_barrier_many_rounds():
+    res, _ = run_ranks(4, "barrier", faults={r: {"rounds": 200} for r in range(4)})
+    assert all(v["ok"] == 1 and v["status"]["code"] == 0 for v in res.values())
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_tree_allreduce_on_cpu_ranks(W):
+    n = 1 << 14
+    xs = [np.random.default_rng(r).standard_normal(n).astype(np.float32) for r in range(W)]
+    res, outs = run_ranks(W, "tree", numel=n, inputs=xs, faults={r: {"chunk": 1 << 9} for r in range(W)})
+    assert all(v["ok"] == 1 for v in res.values()), res
+    ref = np.sum(np.stack(xs).astype(np.float64), 0)
+    for o in outs:
+        np.testing.assert_allclose(o, ref, rtol=1e-5, atol=1e-5)
+        assert np.array_equal(o, outs[0])
+
+
+def test_lost_signal_becomes_a_timeout_that_names_the_peer():
+    t0 = time.time()
+    res, _ = run_ranks(4, "barrier", timeout_ms=300, faults={1: {"drop_signal_to": 2}})
+    assert time.time() - t0 < 20
+    st = res[2]["status"]
+    assert res[2]["ok"] == 0 and st["code"] == 1 and st["where"] == "TCCL_W_BARRIER" and st["peer"] == 1 and st["aborted"]
+    for r in (0, 1, 3):  # a single round: the others did get every signal
+        assert res[r]["ok"] == 1
+
+
+def test_stalled_rank_within_the_limit_is_not_a_failure():
+    res, _ = run_ranks(4, "barrier", timeout_ms=3000, faults={3: {"stall_ms": 300}})
+    assert all(v["ok"] == 1 for v in res.values())
+
+
+def test_rank_that_never_joins():
+    res, _ = run_ranks(4, "barrier", timeout_ms=300, faults={2: {"never_join": True}})
+    for r in (0, 1, 3):
+        st = res[r]["status"]
+        assert res[r]["ok"] == 0 and st["code"] == 1 and st["peer"] == 2
+
+
+def test_rank_that_stops_mid_all_reduce():
+    """Rank 2 stops after three chunks: its tree neighbours time out in the up or
+    down phase, everybody returns, nobody hangs."""
+    W, n = 4, 1 << 14
+    xs = [np.ones(n, np.float32) * r for r in range(W)]
+    t0 = time.time()
+    res, _ = run_ranks(W, "tree", numel=n, inputs=xs, timeout_ms=400,
+                       faults={r: ({"chunk": 1 << 9, "stop_after_chunk": 3} if r == 2 else {"chunk": 1 << 9})
+                               for r in range(W)})
+    assert time.time() - t0 < 30
+    failed = [r for r in range(W) if res[r]["ok"] == 0]
+    assert failed, res
+    wheres = {res[r]["status"]["where"] for r in failed if res[r]["status"]["code"]}
+    assert wheres & {"TCCL_W_TREE_UP", "TCCL_W_TREE_DOWN", "TCCL_W_BARRIER"}
