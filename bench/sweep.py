@@ -36,6 +36,8 @@ def nvlink_bytes_in(coll, algo, W, S):
     if coll == "allreduce":
         if algo == "twoshot_nvls":
             return S + S // W  # reduced slice in + every slice broadcast back (own included)
+        if algo.startswith("push"):
+            return (W - 1) * S
         if algo == "oneshot_nvls":
             return S
         if algo == "oneshot_p2p":
@@ -155,8 +157,11 @@ def main():
             if a.algos == "auto":
                 if coll == "allreduce":
                     algos = (["oneshot_p2p"] if S <= (8 << 20) else []) + ["twoshot_p2p"]
+                    push_ok = S % 16 == 0 and 2 * W * S <= w.ll_bytes
+                    algos += ["push_p2p"] if push_ok else []
                     if w.has_nvls:
                         algos += (["oneshot_nvls"] if S <= (8 << 20) else []) + ["twoshot_nvls"]
+                        algos += ["push_nvls"] if push_ok else []
                     algos += ["tree"] if S >= 4096 else []
                 elif coll == "allgather":
                     algos = ["pull", "push"] + (["push_nvls"] if w.has_nvls else [])
@@ -166,7 +171,7 @@ def main():
                 algos = a.algos.split(",")
             for algo in algos:
                 if coll == "allreduce":
-                    if algo.startswith("oneshot"):
+                    if algo.startswith("oneshot") or algo.startswith("push"):
                         o = torch.empty_like(x)
                         fn = lambda: tccl.all_reduce(x, out=o, algo=algo)
                     elif algo == "tree":

@@ -207,6 +207,77 @@ struct AllReduceOneShotNvls {
   }
 };
 
+// --------------------------------------------- one-shot all-reduce, push variant
+// Latency path for small messages.  Every rank stores its input into slot
+// [parity][rank] of every rank's staging area (posted stores, or one
+// multimem.st), then ONE barrier both publishes the data and tells everybody it
+// is there, and each rank sums the W slots out of its OWN memory.  Compared with
+// the pull variant this drops a barrier round and replaces the peer-load round
+// trip by local loads.  No exit barrier is needed: the two parities alternate
+// from call to call (the parity is the low bit of the barrier epoch), and a rank
+// can only be two calls ahead of a peer after a barrier that the peer has
+// reached, i.e. after the peer has finished reading the slot being reused.  The
+// input does not have to live in symmetric memory.
+// `out_peer[p]` / `mc_out` carry the staging region of rank p / its multicast alias.
+template <typename T, int W, bool kNvls>
+struct AllReduceOneShotPush {
+  using Args = tccl_coll_args;
+  static constexpr int kMaxThreads = 512, kMinBlocks = 1;
+  static constexpr int kMaxW = W ? W : TCCL_MAX_WORLD;
+  static constexpr int U = 2;
+  static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
+    const uint64_t deadline = globaltimer() + c.timeout_ns;
+    const int world = WorldOf<W>::get(c);
+    constexpr int VPT = VecOf<T>::n;
+    const uint64_t nvec = a.numel / VPT;  // the host guarantees a whole number of vectors
+    const uint64_t slot = nvec * 16;
+    const uint64_t bs = blockDim.x;
+    const bool nvls_bar = (a.flags & TCCL_F_NVLS_BARRIER) != 0;
+    const uint32_t e = (nvls_bar ? c.local[TCCL_LOCAL_MCEPOCH + bid] : c.local[TCCL_LOCAL_EPOCH + bid]) + 1u;
+    const uint64_t base = (uint64_t)(e & 1u) * world * slot;
+    const char* src = reinterpret_cast<const char*>(a.in[c.rank]);
+    const uint64_t mine = base + (uint64_t)c.rank * slot;
+    TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint64_t i = i0 + u * bs;
+        if (i < nvec) {
+          const Vec16 v = ld_peer(src + i * 16);
+          if (kNvls) {
+            multimem_st(reinterpret_cast<char*>(a.mc_out) + mine + i * 16, v);
+          } else {
+#pragma unroll
+            for (int p = 0; p < kMaxW; ++p)
+              if (p < world) st_peer(reinterpret_cast<char*>(a.out_peer[p]) + mine + i * 16, v);
+          }
+        }
+      }
+    }
+    barrier_any(c, bid, deadline, nvls_bar);  // data of all ranks for this CTA's slabs has landed here
+    const char* local = reinterpret_cast<const char*>(a.out_peer[c.rank]) + base;
+    TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
+      Vec16 v[kMaxW][U];
+#pragma unroll
+      for (int p = 0; p < kMaxW; ++p)
+        if (p < world) {
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * bs < nvec) v[p][u] = ld_peer(local + (uint64_t)p * slot + (i0 + u * bs) * 16);
+        }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * bs < nvec) {
+          Acc<T> acc;
+          acc.zero();
+#pragma unroll
+          for (int p = 0; p < kMaxW; ++p)
+            if (p < world) acc.add(v[p][u]);
+          st_local(vptr<T>(a.out, i0 + u * bs), acc.pack());
+        }
+    }
+  }
+};
+
 // ---------------------------------------------------- two-shot all-reduce, P2P
 // Rank r sums vector slice r of all W inputs and writes the result straight
 // into slice r of every rank's destination (`out_peer`; the inputs themselves
@@ -462,6 +533,8 @@ template <typename T, int W> using AgPushP2P = AllGatherPush<T, W, false>;
 template <typename T, int W> using AgPushNvls = AllGatherPush<T, W, true>;
 template <typename T, int W> using RsP2P = ReduceScatter<T, W, false>;
 template <typename T, int W> using RsNvls = ReduceScatter<T, W, true>;
+template <typename T, int W> using ArPushP2P = AllReduceOneShotPush<T, W, false>;
+template <typename T, int W> using ArPushNvls = AllReduceOneShotPush<T, W, true>;
 
 }  // namespace tccl
 
@@ -504,6 +577,8 @@ int tccl_wait_never(const tccl_comm* comm, const tccl_barrier_args* args, const 
   }
 TCCL_COLL(tccl_allreduce_oneshot_p2p, AllReduceOneShotP2P)
 TCCL_COLL(tccl_allreduce_oneshot_nvls, AllReduceOneShotNvls)
+TCCL_COLL(tccl_allreduce_push_p2p, ArPushP2P)
+TCCL_COLL(tccl_allreduce_push_nvls, ArPushNvls)
 TCCL_COLL(tccl_allreduce_twoshot_p2p, AllReduceTwoShotP2P)
 TCCL_COLL(tccl_allreduce_twoshot_nvls, AllReduceTwoShotNvls)
 TCCL_COLL(tccl_allgather_pull_p2p, AllGatherPullP2P)

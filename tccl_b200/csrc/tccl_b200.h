@@ -134,6 +134,11 @@ int tccl_wait_never(const tccl_comm*, const tccl_barrier_args*, const tccl_launc
 /* ---- data collectives ------------------------------------------------- */
 int tccl_allreduce_oneshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_oneshot_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+/* small-message latency path: push into the peers' staging slots, one barrier, local sum.
+ * out_peer[p] / mc_out = rank p's slot region (2 parities x world x message bytes) / its multicast
+ * alias; in[rank] = the local input (any device memory); numel * sizeof(T) % 16 == 0 */
+int tccl_allreduce_push_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allreduce_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_twoshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_twoshot_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_pull_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);

@@ -32,6 +32,8 @@ __all__ = [
 ]
 
 _AR_KERNELS = {
+    "push_p2p": "tccl_allreduce_push_p2p",
+    "push_nvls": "tccl_allreduce_push_nvls",
     "oneshot_p2p": "tccl_allreduce_oneshot_p2p",
     "oneshot_nvls": "tccl_allreduce_oneshot_nvls",
     "twoshot_p2p": "tccl_allreduce_twoshot_p2p",
@@ -124,6 +126,8 @@ def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -
     nvls = world.has_nvls
     if world.world_size == 1:
         return "oneshot_p2p"
+    if nbytes <= cfg.push_max_bytes and nbytes % 16 == 0 and 2 * world.world_size * nbytes <= world.ll_bytes:
+        return "push_nvls" if nvls and world.world_size > 2 else "push_p2p"
     if not symmetric_dst or nbytes <= cfg.oneshot_max_bytes:
         return "oneshot_nvls" if nvls and world.world_size > 2 and nbytes <= 4 * cfg.oneshot_max_bytes else "oneshot_p2p"
     return "twoshot_nvls" if nvls and world.world_size > 2 else "twoshot_p2p"
@@ -151,7 +155,55 @@ def all_reduce(x, out=None, *, inplace: bool = False, algo: str = "auto", world:
                    lambda: _plan_all_reduce(w, x, out, inplace, algo, sync_exit))
 
 
+def _plan_push(w, x, out, inplace, algo) -> Plan:
+    """Small-message push all-reduce: the input may be any device tensor."""
+    locs = {r: (x if w.plans is not None else x[r]) for r in w.local_ranks}
+    x0 = locs[w.local_ranks[0]]
+    dt = dtype_code(x0.dtype)
+    nbytes = x0.numel() * x0.element_size()
+    W = w.world_size
+    if not x0.is_contiguous() or x0.data_ptr() % 16 or nbytes % 16:
+        raise ValueError("push all-reduce needs a contiguous, 16-byte aligned input of a multiple of 16 bytes")
+    if 2 * W * nbytes > w.ll_bytes:
+        raise ValueError(f"push all-reduce handles at most {w.ll_bytes // (2 * W)} bytes per rank")
+    if algo == "push_nvls" and not w.has_nvls:
+        raise RuntimeError("push_nvls needs NVLS multicast")
+    slots, mc = w.ll_ptrs(), w.ll_mc()
+    args = {}
+    for r in w.local_ranks:
+        a = L.CollArgs()
+        a.inp[r] = locs[r].data_ptr()
+        for p, v in enumerate(slots):
+            a.out_peer[p] = v
+        a.mc_out = mc
+        a.numel, a.dtype, a.flags = x0.numel(), dt, w.coll_flags()
+        args[r] = a
+    nvec = nbytes // 16
+    block = 256 if nvec <= 2048 else 512
+    grid = grid_for(w, nvec, block, 2, cap=32)
+    go = w.prepare(_AR_KERNELS[algo], args, grid, block, dt)
+    if inplace:
+        for r, a in args.items():
+            a.out = locs[r].data_ptr()  # each vector is read (into the slots) before the barrier, written after
+        return Plan(w, go, args, result=x)
+    if out is not None:
+        for r, a in args.items():
+            o = w.local(out, r)
+            _check_out(o, locs[r])
+            a.out = o.data_ptr()
+        return Plan(w, go, args, result=out)
+    return Plan(w, go, args, alloc=lambda r: torch.empty_like(locs[r]))
+
+
 def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
+    if algo.startswith("push"):
+        return _plan_push(w, x, out, inplace, algo)
+    if algo == "auto":
+        x00 = x if w.plans is not None else x[w.local_ranks[0]]
+        nb0 = x00.numel() * x00.element_size()
+        cand = choose_all_reduce_algo(w, nb0, True)
+        if cand.startswith("push") and x00.is_contiguous() and x00.data_ptr() % 16 == 0:
+            return _plan_push(w, x, out, inplace, cand)
     check_sym_tensor(w, x, "all_reduce input")
     x0 = w.local(x, w.local_ranks[0])
     dt = dtype_code(x0.dtype)
@@ -160,6 +212,8 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
     sym_dst = inplace or out_is_sym
     if algo == "auto":
         algo = choose_all_reduce_algo(w, nbytes, sym_dst)
+        if algo.startswith("push"):  # not eligible after all (alignment): fall back to the pull one-shot
+            algo = "oneshot_nvls" if w.has_nvls and w.world_size > 2 else "oneshot_p2p"
     if algo not in _AR_KERNELS:
         raise ValueError(f"unknown all-reduce algo {algo!r}")
     if algo.endswith("nvls") and not w.has_nvls:

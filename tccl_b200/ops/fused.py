@@ -59,7 +59,7 @@ def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
     lib.tccl_gemm_rs_stage_bytes.restype = C.c_uint64
     lib.tccl_gemm_rs_param_bytes.restype = C.c_uint64
     need = lib.tccl_gemm_rs_stage_bytes(M, N, W)
-    stage_bytes = w.config.stage_mb << 20
+    stage_bytes = (w.config.stage_mb << 20) - w.ll_bytes
     if need > stage_bytes:
         raise ValueError(f"staging area too small: need {need >> 20} MiB, have {w.config.stage_mb} MiB "
                          "(raise TCCL_STAGE_MB)")

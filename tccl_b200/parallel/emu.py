@@ -71,6 +71,7 @@ class EmuWorld(WorldBase):
         self.flags = [torch.zeros(self._flag_words, dtype=torch.int32, device=self.device) for _ in range(W)]
         self.stages = [torch.empty(self._stage_bytes, dtype=torch.uint8, device=self.device) for _ in range(W)]
         self.local_states = [torch.zeros(K["TCCL_LOCAL_WORDS"], dtype=torch.int32, device=self.device) for _ in range(W)]
+        self.ll_bytes = min(2 << 20, self._stage_bytes // 4)
         self._keep = []
         self.plans = None  # emulated launches are not cached
         self._upload_comms()
@@ -87,7 +88,7 @@ class EmuWorld(WorldBase):
             c.mc_flags = 0
             c.mc_stage = 0
             c.local = self.local_states[r].data_ptr()
-            c.stage_bytes = self._stage_bytes
+            c.stage_bytes = self._stage_bytes - self.ll_bytes
             c.timeout_ns = self.config.timeout_ns
         self._comms_host = arr
         self.comms_dev = self._to_device(arr)
@@ -130,6 +131,13 @@ class EmuWorld(WorldBase):
         return [s.data_ptr() for s in self.stages]
 
     def stage_mc(self) -> int:
+        return 0
+
+    def ll_ptrs(self) -> List[int]:
+        off = self._stage_bytes - self.ll_bytes
+        return [s.data_ptr() + off for s in self.stages]
+
+    def ll_mc(self) -> int:
         return 0
 
     def resident_cta_limit(self, block: int) -> int:

@@ -157,7 +157,10 @@ class RealWorld(WorldBase):
         comm.mc_flags = mc if mc else 0
         comm.mc_stage = (mc + self._flag_bytes) if mc else 0
         comm.local = self.local_state.data_ptr()
-        comm.stage_bytes = self._stage_bytes
+        # the tail of the staging area belongs to the small-message push all-reduce (it runs
+        # without an entry barrier, so it must not share slots with the fused GEMM kernels)
+        self.ll_bytes = min(2 << 20, self._stage_bytes // 4)
+        comm.stage_bytes = self._stage_bytes - self.ll_bytes
         comm.timeout_ns = self.config.timeout_ns
         self.comm = comm
         self._stage_ptrs = [ptrs[p] + self._flag_bytes for p in range(self.world_size)]
@@ -226,6 +229,13 @@ class RealWorld(WorldBase):
 
     def stage_mc(self) -> int:
         return self._stage_mc if self._nvls else 0
+
+    def ll_ptrs(self) -> List[int]:
+        off = self._stage_bytes - self.ll_bytes
+        return [p + off for p in self._stage_ptrs]
+
+    def ll_mc(self) -> int:
+        return (self._stage_mc + self._stage_bytes - self.ll_bytes) if self._nvls and self._stage_mc else 0
 
     def stage_view(self, nbytes: int, dtype=torch.uint8, offset: int = 0) -> torch.Tensor:
         """A local tensor view of this rank's staging area."""

@@ -61,6 +61,7 @@ def main():
 
     nvls = w.has_nvls
     ar_algos = ["oneshot_p2p", "twoshot_p2p"] + (["oneshot_nvls", "twoshot_nvls"] if nvls else [])
+    push_algos = ["push_p2p"] + (["push_nvls"] if nvls else [])
 
     # barriers
     case("barrier_p2p", lambda: tccl.barrier(blocks=8, threads=64, rounds=20))
@@ -94,6 +95,16 @@ def main():
                     tccl.all_reduce(x, inplace=True, algo=algo)
                     return close(x, ref, dtype, W, ulps)
                 case(f"allreduce/{algo}/{dtype}/{n}", ar)
+            if n * x.element_size() % 16 == 0 and 2 * W * n * x.element_size() <= w.ll_bytes:
+                for algo in push_algos:
+                    def push_ar(algo=algo):
+                        ok = True
+                        plain = xs[rank].cuda()  # ordinary (non symmetric) memory
+                        for _ in range(3):
+                            out = tccl.all_reduce(plain, algo=algo)
+                            ok = ok and close(out, ref, dtype, W)
+                        return ok
+                    case(f"allreduce/{algo}/{dtype}/{n}", push_ar)
             if n % (W * 8) == 0:
                 for algo in ["p2p"] + (["nvls"] if nvls else []):
                     def rs(algo=algo):
@@ -186,6 +197,31 @@ def main():
         return ok
     case("allreduce/tree", tree)
 
+    def graph_replay():
+        """A captured collective replays correctly (all sync state lives on the device)."""
+        n = 1 << 14
+        x = w.empty(n, torch.float32)
+        o = torch.empty_like(x)
+        x.fill_(float(rank + 1))
+        algos = ["oneshot_p2p", "push_p2p"] + (["twoshot_nvls"] if nvls else ["twoshot_p2p"])
+        ok = True
+        for algo in algos:
+            y = w.empty(n, torch.float32) if algo.startswith("twoshot") else o
+            fn = (lambda: tccl.all_reduce(x, out=y, algo=algo))
+            fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            for it in range(5):
+                x.fill_(float((rank + 1) * (it + 1)))
+                g.replay()
+                torch.cuda.synchronize()
+                ok = ok and bool((y == float((it + 1) * W * (W + 1) // 2)).all())
+        return ok
+    case("cuda_graph_replay", graph_replay)
+
     # back-to-back stress with changing data (WAR/RAW hazards)
     def stress():
         n = 4096
@@ -193,8 +229,8 @@ def main():
         ok = True
         for it in range(300):
             x.fill_(float(it * (rank + 1)))
-            algo = ar_algos[it % len(ar_algos)]
-            if algo.startswith("oneshot"):
+            algo = (ar_algos + push_algos)[it % len(ar_algos + push_algos)]
+            if algo.startswith("oneshot") or algo.startswith("push"):
                 o = tccl.all_reduce(x, algo=algo)
             else:
                 o = tccl.all_reduce(x, inplace=True, algo=algo)
