@@ -26,8 +26,8 @@ class Config:
     timeout_ms: float = 5000.0        # bound of every device-side wait
     max_ctas: int = 0                 # CTAs per collective; 0 = one per SM
     block: int = 512                  # threads per CTA of the data collectives
-    nvls_ctas: int = 16               # CTAs of the NVLS two-shot all-reduce (the switch saturates early;
-                                      # measured on 8xB200: 8-32 CTAs are best, 148 lose a third at 1 GiB)
+    nvls_ctas: int = 8                # CTAs of the NVLS two-shot all-reduce (the switch saturates early;
+                                      # measured on 8xB200: 4-8 CTAs are best from 8 MiB up, 148 lose a third at 1 GiB)
     stage_mb: int = 128               # symmetric staging area per rank
     disable_nvls: bool = False        # never pick a multimem variant
     nvls_barrier: bool = False        # barrier flavour used inside data kernels
