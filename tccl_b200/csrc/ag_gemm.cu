@@ -30,6 +30,7 @@ struct alignas(64) AgGemmParams {
   __nv_bfloat16* out;
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank, comm_ctas;
+  uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop)
   int swiglu;  // 1: columns [0,128) of every 256-wide tile are gate, [128,256) up; out = silu(gate) * up
 };
 
@@ -59,6 +60,7 @@ struct AgGemmPolicy {
     nt = v % tn;
     return true;
   }
+  __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
   __device__ __forceinline__ bool before_load(int mt, int, const Abort& ab) const {
     const int src = mt / p->tiles_m_per_rank;
     if (src == c->rank) return true;
@@ -79,7 +81,7 @@ struct AgGemmPolicy {
       y = mt * BM;
     }
   }
-  __device__ __forceinline__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort&) const {
+  __device__ __forceinline__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort&, const SmemLayout&) const {
     const int row = mt * BM + quad * 32 + lane;
     __nv_bfloat16* crow = p->out + (size_t)row * p->ldo;
     if (p->swiglu) {
@@ -195,7 +197,7 @@ __device__ __forceinline__ void ag_gemm_body(const tccl_comm& c, const AgGemmPar
       tma_prefetch_desc(&p.map_a_shard);
       tma_prefetch_desc(&p.map_a_full);
     }
-    run_mainloop(&p.map_b, p.shp, pol, &c, c.timeout_ns);
+    run_mainloop(&p.map_b, p.shp, pol, &c, c.timeout_ns, p.trace ? p.trace + (size_t)bid * 64 : nullptr);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -236,6 +238,7 @@ static int fill_params(AgGemmParams* p, const tccl_ag_gemm_args* g, int world, i
   for (int q = 0; q < TCCL_MAX_WORLD; ++q) p->a_full[q] = reinterpret_cast<char*>(g->a_full[q]);
   p->mc_a_full = reinterpret_cast<char*>(g->mc_a_full);
   p->out = reinterpret_cast<__nv_bfloat16*>(g->out);
+  p->trace = reinterpret_cast<uint64_t*>(g->trace);
   p->lda_shard = g->lda_shard;
   p->lda_full = g->lda_full;
   p->ldo = g->ldo;

@@ -20,12 +20,13 @@ struct PlainPolicy {
     nt = t - mt * tiles_n;
     return true;
   }
+  __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
   __device__ __forceinline__ bool before_load(int, int, const Abort&) const { return true; }
   __device__ __forceinline__ void a_tile(int mt, const CUtensorMap*& map, int& y) const {
     map = map_a;
     y = mt * BM;
   }
-  __device__ __forceinline__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort&) const {
+  __device__ __forceinline__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort&, const SmemLayout&) const {
     const int row = mt * BM + quad * 32 + lane;
     __nv_bfloat16* crow = C + (size_t)row * ldc;
 #pragma unroll 1

@@ -31,6 +31,7 @@ struct alignas(64) GemmRsParams {
   int ldo;
   int tiles_n;
   int tiles_m_per_rank;
+  uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop)
 };
 
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -41,6 +42,7 @@ struct GemmRsPolicy {
   int bid, nb;
   uint32_t epoch;
   int tpo;  // tiles per owner
+  uint32_t* pending_flag;  // epilogue issuer only: flag of the last pushed tile, raised once its copies are done
 
   __device__ __forceinline__ bool tile(int i, int& mt, int& nt) const {
     const int t = bid + i * nb;
@@ -63,24 +65,60 @@ struct GemmRsPolicy {
     return (uint32_t)(((cg * 4 + v) * BM + row) * 16);
   }
 
-  __device__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort& ab) const {
+  // Raise the flag of the previously pushed tile: its bulk copies must be complete (not
+  // just read out of shared memory) before the release store.
+  __device__ __forceinline__ void flush_pending() {
+    if (pending_flag) {
+      bulk_wait<0>();
+      fence_proxy_async();
+      st_release_sys(pending_flag, epoch);
+      pending_flag = nullptr;
+    }
+  }
+  __device__ __forceinline__ void epilogue_finish(int quad, int lane, const Abort&) {
+    if (quad == 0 && lane == 0) flush_pending();
+  }
+
+  __device__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort& ab, const SmemLayout& sm) {
     const int W = c->world, me = c->rank;
     const int owner = mt / p->tiles_m_per_rank;
     const int lt = (mt - owner * p->tiles_m_per_rank) * p->tiles_n + nt;
     const int row = quad * 32 + lane;
+    const bool issuer = quad == 0 && lane == 0;
+    // first of all publish the previous pushed tile: a rank that sat on a pending flag while
+    // waiting for its peers' flags would deadlock with peers doing the same
+    if (issuer) flush_pending();
     if (owner != me) {
+      // Remote tile: tensor memory -> registers -> an 8 KB shared-memory chunk per 32 columns
+      // (already in the slot's layout) -> ONE bulk async copy to the owner's staging slot.  The
+      // copy engine keeps the NVLink writes in flight; the four epilogue warps are free again
+      // after ~3 us instead of pacing 64 KB of posted 16-byte stores themselves (measured:
+      // 21 us per tile, which made the whole kernel store-issue-bound).
       char* slot = c->stage[owner] + ((size_t)me * tpo + lt) * kSlotBytes;
 #pragma unroll 1
       for (int cg = 0; cg < BN / 32; ++cg) {
+        uint8_t* buf = sm.epi[cg & 1];
+        if (cg >= 2) {
+          if (issuer) bulk_wait_read<1>();  // the copy that last used this chunk has read it
+          epi_bar();
+        }
         uint32_t r[32];
         tmem_ld_32x32(taddr + cg * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int v = 0; v < 4; ++v) st_peer(slot + slot_off(row, cg, v), pack8_bf16(r + v * 8));
+        for (int v = 0; v < 4; ++v) st_shared_v4(buf + (v * BM + row) * 16, pack8_bf16(r + v * 8));
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk copy
+        epi_bar();
+        if (issuer) {
+          bulk_store(slot + (size_t)cg * kEpiChunkBytes, buf, kEpiChunkBytes);
+          bulk_commit();
+        }
       }
-      epi_bar();  // all 128 threads' stores are issued before the release below
-      if (quad == 0 && lane == 0)
-        st_release_sys(c->flags[owner] + TCCL_FLAG_TILE + me * TCCL_MAX_TILES + lt, epoch);
+      if (issuer) {
+        bulk_wait_read<0>();  // both chunks are free for the next tile
+        pending_flag = c->flags[owner] + TCCL_FLAG_TILE + me * TCCL_MAX_TILES + lt;
+      }
+      epi_bar();
       return true;
     }
     // own tile: gather the peers' partials
@@ -154,9 +192,10 @@ __device__ __forceinline__ void gemm_rs_body(const tccl_comm& c, const GemmRsPar
   pol.nb = nb;
   pol.epoch = c.local[TCCL_LOCAL_TILE_EPOCH] + 1u;
   pol.tpo = p.tiles_m_per_rank * p.tiles_n;
+  pol.pending_flag = nullptr;
   barrier_p2p(c, bid, deadline);  // the previous call's staging slots are free on every rank
   if (threadIdx.x == 0) tma_prefetch_desc(&p.map_a);
-  run_mainloop(&p.map_b, p.shp, pol, &c, c.timeout_ns);
+  run_mainloop(&p.map_b, p.shp, pol, &c, c.timeout_ns, p.trace ? p.trace + (size_t)bid * 64 : nullptr);
   // the last CTA of this rank to finish publishes the new epoch for the next call
   if (threadIdx.x == 0) {
     __threadfence();
@@ -187,6 +226,7 @@ static int fill_params(GemmRsParams* p, const tccl_gemm_rs_args* g, int world) {
   if (rc) return rc;
   p->shp = Shape{g->m, g->n, g->k};
   p->out = reinterpret_cast<__nv_bfloat16*>(g->out);
+  p->trace = reinterpret_cast<uint64_t*>(g->trace);
   p->ldo = g->ldo;
   p->tiles_n = g->n / BN;
   p->tiles_m_per_rank = g->m / world / BM;

@@ -31,7 +31,10 @@ constexpr int kEpiWarp0 = 4;  // first epilogue warp
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kABytes = BM * BK * 2, kBBytes = BN * BK * 2;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr size_t kSmemBytes = 1024 /*align slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/;
+// epilogue staging: two 8 KB chunks (32 columns x 128 rows of bf16) that bulk async copies drain
+constexpr uint32_t kEpiChunkBytes = BM * 32 * 2;
+constexpr size_t kSmemBytes =
+    1024 /*align slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/ + 2 * kEpiChunkBytes;
 
 // ------------------------------------------------------------------ PTX
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -64,6 +67,24 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// bulk async copy shared -> global (the destination may be a peer GPU's memory: plain
+// unicast copy, no multicast) and its group bookkeeping
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(void* smem_dst, const Vec16& v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};"
+               ::"r"(smem_u32(smem_dst)), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
@@ -167,6 +188,7 @@ struct SmemLayout {
   uint64_t* tmem_empty;  // [2]
   uint32_t* tmem_base;
   int* abort_flag;
+  uint8_t* epi[2];       // epilogue staging chunks (kEpiChunkBytes each, 128-byte aligned)
   __device__ explicit SmemLayout(uint8_t* raw) {
     uint8_t* p = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
     for (int s = 0; s < kStages; ++s) {
@@ -180,6 +202,8 @@ struct SmemLayout {
     tmem_empty = bars + 2 * kStages + 2;
     tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
     abort_flag = reinterpret_cast<int*>(tmem_base + 1);
+    epi[0] = p + (size_t)kStages * kStageBytes + 256;
+    epi[1] = epi[0] + kEpiChunkBytes;
   }
 };
 
@@ -188,17 +212,21 @@ struct SmemLayout {
 //   Policy::a_tile(m_tile, map, y)           -> which tensor map / row coordinate holds the A rows
 //   Policy::before_load(m_tile, n_tile, ab)  -> runs in the producer thread before the
 //                                               tile's first TMA load (wait for remote rows)
-//   Policy::epilogue(m_tile, n_tile, acc_taddr, quad, lane, ab)
+//   Policy::epilogue(m_tile, n_tile, acc_taddr, quad, lane, ab, sm)
 //                                            -> runs in the 4 epilogue warps
+//   Policy::epilogue_finish(quad, lane, ab)  -> once, in the epilogue warps, after the last tile
 template <class Policy>
 __device__ void run_mainloop(const CUtensorMap* map_b, const Shape shp, Policy& pol, const tccl_comm* comm,
-                             uint64_t timeout_ns) {
+                             uint64_t timeout_ns, uint64_t* trace = nullptr) {
+  // `trace` (optional, this CTA's 64 words): %globaltimer stamps per tile i < 15 —
+  // [4i] producer may load, [4i+1] accumulator ready, [4i+2] epilogue done; [63] kernel start
   extern __shared__ uint8_t smem_raw[];
   SmemLayout sm(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (shp.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
+    if (trace) trace[63] = globaltimer();
     *sm.abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(sm.full + s, 1);
@@ -229,6 +257,7 @@ __device__ void run_mainloop(const CUtensorMap* map_b, const Shape shp, Policy& 
       int mt, nt;
       for (int i = 0; ok && pol.tile(i, mt, nt); ++i) {
         ok = pol.before_load(mt, nt, ab);
+        if (trace && i < 15) trace[4 * i] = globaltimer();
         const CUtensorMap* map_a;
         int ya;
         pol.a_tile(mt, map_a, ya);
@@ -293,10 +322,13 @@ __device__ void run_mainloop(const CUtensorMap* map_b, const Shape shp, Policy& 
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
-      ok = pol.epilogue(mt, nt, taddr, quad, lane, ab);
+      if (trace && i < 15 && quad == 0 && lane == 0) trace[4 * i + 1] = globaltimer();
+      ok = pol.epilogue(mt, nt, taddr, quad, lane, ab, sm);
+      if (trace && i < 15 && quad == 0 && lane == 0) trace[4 * i + 2] = globaltimer();
       tc_fence_before();
       mbar_arrive(sm.tmem_empty + acc);
     }
+    pol.epilogue_finish(quad, lane, ab);
   }
 
   tc_fence_before();

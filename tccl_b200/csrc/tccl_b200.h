@@ -201,6 +201,7 @@ typedef struct tccl_gemm_rs_args {
   void* out;       /* this rank's [m / world, n] result rows */
   int32_t m, n, k; /* m % (world * 128) == 0, n % 256 == 0, k % 8 == 0 */
   int32_t lda, ldb, ldo;
+  void* trace;     /* optional: grid * 64 uint64 words of per-tile %globaltimer stamps, or NULL */
 } tccl_gemm_rs_args;
 /* bytes of staging area (per rank) the fused kernel needs for an m x n product */
 uint64_t tccl_gemm_rs_stage_bytes(int m, int n, int world);
@@ -223,6 +224,7 @@ typedef struct tccl_ag_gemm_args {
   int32_t comm_ctas;                /* CTAs that move the shard; the others run the GEMM */
   int32_t swiglu;                   /* 1: every 256-row block of bt is 128 gate rows then the 128 matching up
                                        rows; out is [m, n / 2] = silu(gate) * up (n % 256 == 0) */
+  void* trace;                      /* optional: grid * 64 uint64 words of per-tile %globaltimer stamps */
 } tccl_ag_gemm_args;
 uint64_t tccl_ag_gemm_param_bytes(void);
 /* same calling convention as tccl_gemm_reduce_scatter */

@@ -27,6 +27,17 @@ def _locals(w: WorldBase, x):
     return {r: x[r] for r in w.local_ranks}
 
 
+def _trace_ptr(w: WorldBase, trace, r: int, grid: int) -> int:
+    """``trace``: an int64 CUDA tensor of at least ``grid * 64`` words (a list of them when
+    emulated) that receives per-tile %globaltimer stamps; None = no tracing."""
+    if trace is None:
+        return 0
+    t = trace if w.plans is not None else trace[r]
+    if t.dtype != torch.int64 or t.numel() < grid * 64 or not t.is_cuda:
+        raise ValueError(f"trace must be an int64 CUDA tensor of >= {grid * 64} words")
+    return t.data_ptr()
+
+
 def _gemm_ctas(w: WorldBase) -> int:
     n = w.config.max_ctas or w.num_sms()
     if w.plans is None:  # emulated ranks share one GPU and each CTA takes a whole SM
@@ -34,7 +45,7 @@ def _gemm_ctas(w: WorldBase) -> int:
     return n
 
 
-def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
+def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBase] = None):
     """``out_r = rows r of sum_ranks (a_rank @ bt_rank.T)`` — tensor-parallel
     down-projection fused with the reduce-scatter over token rows.
 
@@ -64,6 +75,7 @@ def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
         raise ValueError(f"staging area too small: need {need >> 20} MiB, have {w.config.stage_mb} MiB "
                          "(raise TCCL_STAGE_MB)")
     outs = {}
+    grid = _gemm_ctas(w)
     Os = _locals(w, out) if out is not None else None
     arr = (L.GemmRsArgs * len(w.local_ranks))()
     for i, r in enumerate(w.local_ranks):
@@ -73,9 +85,8 @@ def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
         o = Os[r] if Os is not None else torch.empty((M // W, N), dtype=torch.bfloat16, device=ar.device)
         outs[r] = o
         arr[i] = L.GemmRsArgs(ar.data_ptr(), br.data_ptr(), o.data_ptr(), M, N, Kr, ar.stride(0), br.stride(0),
-                              o.stride(0))
+                              o.stride(0), _trace_ptr(w, trace, r, grid))
     stream = torch.cuda.current_stream(a0.device).cuda_stream
-    grid = _gemm_ctas(w)
     fn = lib.tccl_gemm_reduce_scatter
     if w.plans is not None:
         l = L.Launch(grid, 256, 0, 0, C.c_void_p(stream))
@@ -94,7 +105,7 @@ def gemm_reduce_scatter(a, bt, out=None, *, world: Optional[WorldBase] = None):
     return [outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]]
 
 
-def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, swiglu: bool = False,
+def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, swiglu: bool = False, trace=None,
                     world: Optional[WorldBase] = None):
     """``out_r = all_gather(a_shard) @ bt_r.T`` — tensor-parallel up-projection
     fused with the all-gather of the token rows.
@@ -160,6 +171,7 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.lda_shard, g.lda_full, g.ldb, g.ldo = ar.stride(0), Kd, br.stride(0), o.stride(0)
         g.comm_ctas = comm_ctas
         g.swiglu = 1 if swiglu else 0
+        g.trace = _trace_ptr(w, trace, r, grid)
         arr[i] = g
     stream = torch.cuda.current_stream(a0.device).cuda_stream
     fn = lib.tccl_allgather_gemm
