@@ -31,6 +31,7 @@ struct alignas(64) AgGemmParams {
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank, comm_ctas;
   uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop)
+  int mc_a_full_only;  // 1: force the LSU / multimem.st movers
   int swiglu;  // 1: columns [0,128) of every 256-wide tile are gate, [128,256) up; out = silu(gate) * up
 };
 
@@ -127,6 +128,90 @@ struct AgGemmPolicy {
   }
 };
 
+// Data movers, bulk-copy form: one thread per mover CTA drives the copy engine.  Rows of the
+// shard are bulk-loaded into a ring of shared-memory slots and bulk-stored from there to the
+// gathered buffer of every rank (plain unicast copies; the peers' memory is only ever written,
+// and never through a multicast TMA operation).  An SM's load/store unit sustains only a few
+// GB/s of posted remote stores (measured ~3 GB/s per 128 threads), so LSU movers need most of
+// the GPU to fill the link; the copy engine lets a handful of CTAs do it and leaves the SMs
+// to the GEMM.
+constexpr int kMoverSlots = 16;
+constexpr uint32_t kMoverSlotBytes = 12 * 1024;  // rows up to 6144 bf16 elements
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__device__ void ag_comm_bulk(const tccl_comm& c, const AgGemmParams& p, int bid, uint32_t epoch) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_abort;
+  const uint64_t deadline = globaltimer() + c.timeout_ns;
+  barrier_p2p(c, bid, deadline);  // every rank is done reading the buffer from the previous call
+  if (threadIdx.x != 0) return;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + (size_t)kMoverSlots * kMoverSlotBytes);
+  s_abort = 0;
+  for (int s = 0; s < kMoverSlots; ++s) mbar_init(bars + s, 1);
+  fence_barrier_init();
+  Abort ab{&s_abort, &c, c.local + TCCL_LOCAL_STATUS, deadline};
+  const int W = c.world, me = c.rank, nc = p.comm_ctas;
+  const uint32_t row_bytes = (uint32_t)p.shp.K * 2;
+  const int rows_per_rank = p.tiles_m_per_rank * BM;
+  uint32_t phases = 0;  // bit s = parity of slot s's mbarrier
+  bool ok = true;
+  // Batches of kBatch rows alternate between the two halves of the slot ring.  While batch j
+  // is being stored, batch j-1 may still be in flight; a row tile is published once the
+  // batch that closed it is known complete, i.e. one batch later (every batch is padded to
+  // exactly kBatch commit groups so that "at most kBatch groups pending" means "all earlier
+  // batches are done").
+  constexpr int kBatch = kMoverSlots / 2;
+  auto publish = [&](int rt) {
+    fence_proxy_async();
+    fence_acq_rel_sys();
+    const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_AGCNT + rt, 1u);
+    if (done == (uint32_t)nc - 1u) {
+      c.local[TCCL_LOCAL_AGCNT + rt] = 0u;
+      fence_acq_rel_sys();
+      for (int q = 0; q < W; ++q) st_release_sys(c.flags[q] + TCCL_FLAG_AG + me * TCCL_MAX_ROW_TILES + rt, epoch);
+    }
+  };
+  int pending_rt = -1;  // row tile closed by the previous batch, not yet published
+  uint32_t batch = 0;
+  for (int rt = 0; rt < p.tiles_m_per_rank && ok; ++rt) {
+    for (int r0 = rt * BM + bid; r0 < (rt + 1) * BM && ok; r0 += nc * kBatch, ++batch) {
+      const int set = (batch & 1) * kBatch;
+      if (batch >= 2) bulk_wait_read<kBatch>();  // batch - 2 has been read out of this half
+      int n = 0;
+      for (int row = r0; row < (rt + 1) * BM && n < kBatch; row += nc, ++n) {
+        mbar_arrive_expect_tx(bars + set + n, row_bytes);
+        bulk_load(base + (size_t)(set + n) * kMoverSlotBytes, p.a_shard + (size_t)row * p.lda_shard * 2, row_bytes,
+                  bars + set + n);
+      }
+      int k = 0;
+      for (int row = r0; row < (rt + 1) * BM && k < kBatch; row += nc, ++k) {
+        const int sl = set + k;
+        ok = mbar_wait(bars + sl, (phases >> sl) & 1u, ab);
+        if (!ok) break;
+        phases ^= 1u << sl;
+        const size_t dst = (size_t)(me * rows_per_rank + row) * p.lda_full * 2;
+        for (int q = 0; q < W; ++q) bulk_store(p.a_full[q] + dst, base + (size_t)sl * kMoverSlotBytes, row_bytes);
+        bulk_commit();
+      }
+      for (; k < kBatch; ++k) bulk_commit();  // pad: empty groups
+      if (!ok) break;
+      if (pending_rt >= 0) {
+        bulk_wait<kBatch>();  // everything before this batch is complete
+        publish(pending_rt);
+        pending_rt = -1;
+      }
+      if (r0 + nc * kBatch >= (rt + 1) * BM) pending_rt = rt;  // this batch closes the row tile
+    }
+  }
+  bulk_wait<0>();
+  if (ok && pending_rt >= 0) publish(pending_rt);
+}
+
 // data movers: CTA b of `comm_ctas` copies its share of every row tile of the shard
 __device__ void ag_comm_part(const tccl_comm& c, const AgGemmParams& p, int bid, uint32_t epoch) {
   __shared__ int s_last;
@@ -185,7 +270,11 @@ __device__ void ag_comm_part(const tccl_comm& c, const AgGemmParams& p, int bid,
 __device__ __forceinline__ void ag_gemm_body(const tccl_comm& c, const AgGemmParams& p, int bid, int nb) {
   const uint32_t epoch = c.local[TCCL_LOCAL_TILE_EPOCH] + 1u;
   if (bid < p.comm_ctas) {
-    ag_comm_part(c, p, bid, epoch);
+    // rows that fit a mover slot go through the copy engine, wider ones through the LSU
+    if ((uint32_t)p.shp.K * 2 <= kMoverSlotBytes && !p.mc_a_full_only)
+      ag_comm_bulk(c, p, bid, epoch);
+    else
+      ag_comm_part(c, p, bid, epoch);
   } else {
     AgGemmPolicy pol;
     pol.c = &c;
@@ -246,6 +335,7 @@ static int fill_params(AgGemmParams* p, const tccl_ag_gemm_args* g, int world, i
   p->tiles_m_per_rank = rows / BM;
   p->comm_ctas = g->comm_ctas;
   p->swiglu = g->swiglu;
+  p->mc_a_full_only = g->lsu_movers;
   if (g->swiglu && (g->n % BN)) return -TCCL_ESIZE;  // whole gate|up tiles only
   if (p->tiles_m_per_rank > TCCL_MAX_ROW_TILES) return -TCCL_ESIZE;
   return 0;

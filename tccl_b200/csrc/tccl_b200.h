@@ -225,6 +225,7 @@ typedef struct tccl_ag_gemm_args {
   int32_t swiglu;                   /* 1: every 256-row block of bt is 128 gate rows then the 128 matching up
                                        rows; out is [m, n / 2] = silu(gate) * up (n % 256 == 0) */
   void* trace;                      /* optional: grid * 64 uint64 words of per-tile %globaltimer stamps */
+  int32_t lsu_movers;               /* 1: move the shard with LSU / multimem.st stores instead of bulk copies */
 } tccl_ag_gemm_args;
 uint64_t tccl_ag_gemm_param_bytes(void);
 /* same calling convention as tccl_gemm_reduce_scatter */

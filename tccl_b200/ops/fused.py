@@ -106,7 +106,7 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBas
 
 
 def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, swiglu: bool = False, trace=None,
-                    world: Optional[WorldBase] = None):
+                    lsu_movers: bool = False, world: Optional[WorldBase] = None):
     """``out_r = all_gather(a_shard) @ bt_r.T`` — tensor-parallel up-projection
     fused with the all-gather of the token rows.
 
@@ -172,6 +172,7 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.comm_ctas = comm_ctas
         g.swiglu = 1 if swiglu else 0
         g.trace = _trace_ptr(w, trace, r, grid)
+        g.lsu_movers = 1 if lsu_movers else 0
         arr[i] = g
     stream = torch.cuda.current_stream(a0.device).cuda_stream
     fn = lib.tccl_allgather_gemm
