@@ -36,7 +36,7 @@ class Config:
     oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
     tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
     tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
-    ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard
+    ag_movers: int = 16                   # all-gather -> GEMM: CTAs that move the shard (two alternating groups)
     debug: bool = False
 
     @classmethod

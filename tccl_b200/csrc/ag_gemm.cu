@@ -217,14 +217,21 @@ __device__ void ag_comm_part(const tccl_comm& c, const AgGemmParams& p, int bid,
   __shared__ int s_last;
   const uint64_t deadline = globaltimer() + c.timeout_ns;
   barrier_p2p(c, bid, deadline);  // every rank is done reading the buffer from the previous call
-  const int W = c.world, me = c.rank, nc = p.comm_ctas;
+  const int W = c.world, me = c.rank;
+  // Two groups of movers take the row tiles alternately: publishing a row tile needs a
+  // system-scope fence that drains the group's stores (a switch round trip), and while one
+  // group drains the other keeps the link busy.
+  const int groups = p.comm_ctas >= 2 ? 2 : 1;
+  const int nc = p.comm_ctas / groups;          // movers per row tile
+  const int grp = bid / nc, gb = bid - grp * nc;  // my group, my index inside it
+  if (grp >= groups) return;                    // odd mover count: the last CTA sits out
   const int K = p.shp.K;
   const int vec_per_row = K / 8;
   const int rows_per_rank = p.tiles_m_per_rank * BM;
-  for (int rt = 0; rt < p.tiles_m_per_rank; ++rt) {
+  for (int rt = grp; rt < p.tiles_m_per_rank; rt += groups) {
     const uint32_t nvec = (uint32_t)BM * vec_per_row;
     const uint32_t per = (nvec + nc - 1) / nc;
-    const uint32_t lo = min(per * bid, nvec), hi = min(lo + per, nvec);
+    const uint32_t lo = min(per * gb, nvec), hi = min(lo + per, nvec);
     // 8 vectors per thread in flight: a mover CTA has to keep ~32 KB on the wire to matter
     constexpr int U = 8;
     for (uint32_t i0 = lo + threadIdx.x; i0 < hi; i0 += U * blockDim.x) {
@@ -270,8 +277,11 @@ __device__ void ag_comm_part(const tccl_comm& c, const AgGemmParams& p, int bid,
 __device__ __forceinline__ void ag_gemm_body(const tccl_comm& c, const AgGemmParams& p, int bid, int nb) {
   const uint32_t epoch = c.local[TCCL_LOCAL_TILE_EPOCH] + 1u;
   if (bid < p.comm_ctas) {
-    // rows that fit a mover slot go through the copy engine, wider ones through the LSU
-    if ((uint32_t)p.shp.K * 2 <= kMoverSlotBytes && !p.mc_a_full_only)
+    // With NVLS one multimem.st reaches all ranks through the switch (egress = the shard, not
+    // W-1 copies of it): the LSU movers win (measured on 8xB200: 117 us against 170-200 us for
+    // bulk copies, which must send every copy themselves).  Without NVLS the copy engine moves
+    // rows that fit a slot.
+    if (!p.mc_a_full && (uint32_t)p.shp.K * 2 <= kMoverSlotBytes && !p.mc_a_full_only)
       ag_comm_bulk(c, p, bid, epoch);
     else
       ag_comm_part(c, p, bid, epoch);
