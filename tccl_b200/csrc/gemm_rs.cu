@@ -1,16 +1,19 @@
 // GEMM -> reduce-scatter in ONE kernel (tensor parallel down-projection):
 //   out_r[M/W, N] = rows [r M/W, (r+1) M/W) of  sum_src  A_src[M, K_src] * Bt_src[N, K_src]^T
 // Every rank runs the tcgen05 mainloop over all M x N tiles of its partial
-// product.  Tiles are ordered by owner, starting with the next rank and ending
-// with the own rows.  The epilogue of a tile owned by a peer stores the bf16
-// partial straight into that peer's staging slot [src][tile] over NVLink
-// (posted 16-byte stores, fully coalesced) and then raises the tile's flag with
-// a release store.  The epilogue of an own tile — computed last, when the peers'
-// partials have mostly landed — waits for the W-1 flags of that tile, adds the
-// W-1 staged partials to its own fp32 accumulator from tensor memory, rounds
-// once and writes the final rows.  The transfer of tile i therefore overlaps
-// the MMAs of tile i+1 (second TMEM accumulator) tile by tile, and the
-// reduction costs no extra kernel and no extra pass over HBM.
+// product, ordered by owner: its own rows first, then the next rank's, and so
+// on.  The epilogue of every tile converts the accumulator to bf16 into an 8 KB
+// shared-memory chunk per 32 columns and hands it to the copy engine: one bulk
+// async copy per chunk into slot [src][tile] of the OWNER's staging area — over
+// NVLink for a peer, locally for the own rows — and, once a tile's copies are
+// complete, a release store raises the tile's flag at the owner.  While tile i
+// is on the wire the MMAs of tile i+1 run (second TMEM accumulator).  When a CTA
+// has issued its last tile it joins the final phase: all CTAs of the rank share
+// out the rank's tiles in 32-row units, wait for the W flags of a unit's tile and
+// sum the W staged partials in fp32 (fixed order) into the output rows.  The
+// reduction is therefore spread over the whole GPU and overlaps the peers' last
+// pushes, instead of sitting in the epilogue of the few CTAs that computed the
+// own rows last.
 //
 // Flags carry the call's epoch (kept in device memory and advanced by the last
 // CTA to finish), so nothing has to be reset and a captured graph can replay.
@@ -48,7 +51,7 @@ struct GemmRsPolicy {
     const int t = bid + i * nb;
     if (t >= c->world * tpo) return false;
     const int j = t / tpo, local = t - j * tpo;
-    int owner = c->rank + 1 + j;
+    int owner = c->rank + j;  // own rows first: they need no link and are reduced last anyway
     if (owner >= c->world) owner -= c->world;
     mt = owner * p->tiles_m_per_rank + local / p->tiles_n;
     nt = local % p->tiles_n;
@@ -80,7 +83,7 @@ struct GemmRsPolicy {
   }
 
   __device__ bool epilogue(int mt, int nt, uint32_t taddr, int quad, int lane, const Abort& ab, const SmemLayout& sm) {
-    const int W = c->world, me = c->rank;
+    const int me = c->rank;
     const int owner = mt / p->tiles_m_per_rank;
     const int lt = (mt - owner * p->tiles_m_per_rank) * p->tiles_n + nt;
     const int row = quad * 32 + lane;
@@ -88,8 +91,8 @@ struct GemmRsPolicy {
     // first of all publish the previous pushed tile: a rank that sat on a pending flag while
     // waiting for its peers' flags would deadlock with peers doing the same
     if (issuer) flush_pending();
-    if (owner != me) {
-      // Remote tile: tensor memory -> registers -> an 8 KB shared-memory chunk per 32 columns
+    {
+      // tensor memory -> registers -> an 8 KB shared-memory chunk per 32 columns
       // (already in the slot's layout) -> ONE bulk async copy to the owner's staging slot.  The
       // copy engine keeps the NVLink writes in flight; the four epilogue warps are free again
       // after ~3 us instead of pacing 64 KB of posted 16-byte stores themselves (measured:
@@ -119,69 +122,56 @@ struct GemmRsPolicy {
         pending_flag = c->flags[owner] + TCCL_FLAG_TILE + me * TCCL_MAX_TILES + lt;
       }
       epi_bar();
-      return true;
+      return !*ab.flag;
     }
-    // own tile: gather the peers' partials
-    if (quad == 0 && lane < W && lane != me) {
-      if (!wait_reach(c->flags[me] + TCCL_FLAG_TILE + lane * TCCL_MAX_TILES + lt, epoch, *c, ab.deadline, lane,
-                      TCCL_W_TILE))
-        *ab.flag = 1;
-    }
-    epi_bar();
-    if (*ab.flag) return false;
-    const int orow = (mt - owner * p->tiles_m_per_rank) * BM + row;
-    __nv_bfloat16* dst = p->out + (size_t)orow * p->ldo + nt * BN;
-    const bool row_ok = mt * BM + row < p->shp.M;
-    // All W-1 staged partials of a 32-column group are requested before any is
-    // consumed: 4 (W-1) 16-byte loads per thread in flight.  A reduction that waits
-    // for each load in turn leaves the epilogue latency-bound (measured: the own
-    // tiles then take as long as the whole GEMM).
-#pragma unroll 1
-    for (int cg = 0; cg < BN / 32; ++cg) {
-      Vec16 x[TCCL_MAX_WORLD - 1][4];
-#pragma unroll
-      for (int j = 0; j < TCCL_MAX_WORLD - 1; ++j) {
-        if (j < W - 1) {
-          const int src = j < me ? j : j + 1;
-          const char* slot = c->stage[me] + ((size_t)src * tpo + lt) * kSlotBytes;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) x[j][v] = ld_peer(slot + slot_off(row, cg, v));
-        }
-      }
-      uint32_t r[32];
-      tmem_ld_32x32(taddr + cg * 32, r);
-      tmem_ld_wait();
-      float* acc = reinterpret_cast<float*>(r);
-#pragma unroll
-      for (int j = 0; j < TCCL_MAX_WORLD - 1; ++j) {
-        if (j < W - 1) {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const Vec16& q = x[j][v];
-            acc[v * 8 + 0] += Acc<__nv_bfloat16>::lo(q.x); acc[v * 8 + 1] += Acc<__nv_bfloat16>::hi(q.x);
-            acc[v * 8 + 2] += Acc<__nv_bfloat16>::lo(q.y); acc[v * 8 + 3] += Acc<__nv_bfloat16>::hi(q.y);
-            acc[v * 8 + 4] += Acc<__nv_bfloat16>::lo(q.z); acc[v * 8 + 5] += Acc<__nv_bfloat16>::hi(q.z);
-            acc[v * 8 + 6] += Acc<__nv_bfloat16>::lo(q.w); acc[v * 8 + 7] += Acc<__nv_bfloat16>::hi(q.w);
-          }
-        }
-      }
-      if (row_ok) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          if (nt * BN + cg * 32 + v * 8 < p->shp.N) {
-            Vec16 o;
-            o.x = Acc<__nv_bfloat16>::pk(acc[v * 8 + 0], acc[v * 8 + 1]);
-            o.y = Acc<__nv_bfloat16>::pk(acc[v * 8 + 2], acc[v * 8 + 3]);
-            o.z = Acc<__nv_bfloat16>::pk(acc[v * 8 + 4], acc[v * 8 + 5]);
-            o.w = Acc<__nv_bfloat16>::pk(acc[v * 8 + 6], acc[v * 8 + 7]);
-            st_local(dst + cg * 32 + v * 8, o);
-          }
-        }
-      }
-    }
-    return true;
   }
 };
+
+// Final phase, all threads of all CTAs: unit u = (own tile lt, 32-row quarter).  Thread t of
+// the CTA owns (16-byte column group t / 32 [+ 8 per pass], row t % 32): for a fixed column
+// group the 32 rows of a quarter are 512 contiguous bytes of every slot.
+__device__ void rs_final_reduce(const tccl_comm& c, const GemmRsParams& p, int bid, int nb, uint32_t epoch, int tpo,
+                                uint64_t deadline) {
+  const int W = c.world, me = c.rank;
+  const int t = threadIdx.x;
+  for (int u = bid; u < tpo * 4; u += nb) {
+    const int lt = u >> 2, qr = u & 3;
+    int ok = 1;
+    if (t < W)
+      ok = wait_reach(c.flags[me] + TCCL_FLAG_TILE + t * TCCL_MAX_TILES + lt, epoch, c, deadline, t, TCCL_W_TILE);
+    if (!__syncthreads_and(ok)) return;
+    const int mtl = lt / p.tiles_n, nt = lt - mtl * p.tiles_n;
+    const int row = qr * 32 + (t & 31);
+    const int orow = mtl * BM + row;
+    __nv_bfloat16* dst = p.out + (size_t)orow * p.ldo + nt * BN;
+    const bool row_ok = me * p.tiles_m_per_rank * BM + orow < p.shp.M;
+    const char* slot0 = c.stage[me] + (size_t)lt * kSlotBytes;
+    const size_t src_stride = (size_t)tpo * kSlotBytes;
+    // two passes (column groups) at a time: 2 W 16-byte loads per thread in flight
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      Vec16 x[2][TCCL_MAX_WORLD];
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int cgv = (t >> 5) + 8 * (2 * half + q);  // 0..31 = (32-column group) * 4 + vector
+        const uint32_t off = (uint32_t)((cgv * BM + row) * 16);
+#pragma unroll
+        for (int src = 0; src < TCCL_MAX_WORLD; ++src)
+          if (src < W) x[q][src] = ld_peer(slot0 + src * src_stride + off);
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int cgv = (t >> 5) + 8 * (2 * half + q);
+        Acc<__nv_bfloat16> acc;
+        acc.zero();
+#pragma unroll
+        for (int src = 0; src < TCCL_MAX_WORLD; ++src)
+          if (src < W) acc.add(x[q][src]);
+        if (row_ok && nt * BN + cgv * 8 < p.shp.N) st_local(dst + cgv * 8, acc.pack());
+      }
+    }
+  }
+}
 
 __device__ __forceinline__ void gemm_rs_body(const tccl_comm& c, const GemmRsParams& p, int bid, int nb) {
   const uint64_t deadline = globaltimer() + c.timeout_ns;
@@ -196,6 +186,8 @@ __device__ __forceinline__ void gemm_rs_body(const tccl_comm& c, const GemmRsPar
   barrier_p2p(c, bid, deadline);  // the previous call's staging slots are free on every rank
   if (threadIdx.x == 0) tma_prefetch_desc(&p.map_a);
   run_mainloop(&p.map_b, p.shp, pol, &c, c.timeout_ns, p.trace ? p.trace + (size_t)bid * 64 : nullptr);
+  rs_final_reduce(c, p, bid, nb, pol.epoch, pol.tpo, deadline);
+  if (p.trace && threadIdx.x == 0) p.trace[(size_t)bid * 64 + 62] = globaltimer();
   // the last CTA of this rank to finish publishes the new epoch for the next call
   if (threadIdx.x == 0) {
     __threadfence();
