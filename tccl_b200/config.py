@@ -34,6 +34,8 @@ class Config:
     force_variant: str = ""           # e.g. "oneshot_p2p"; empty = size-based choice
     push_max_bytes: int = 64 * 1024       # all-reduce: push variant (one barrier, local sum) up to here
     oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
+    staged_twoshot: bool = True           # large all-reduce into ordinary memory: two-shot via a cached symmetric buffer
+    staged_max_bytes: int = 1 << 30       # ... up to this message size (the buffer is kept per size and dtype)
     tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
     tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);

@@ -111,8 +111,6 @@ typedef struct tccl_launch {
 int tccl_version(void);
 const char* tccl_error_string(int code);
 int tccl_num_sms(void);
-/* occupancy-limited CTAs per SM for kernel `name` at `block` threads (0 if unknown) */
-int tccl_max_ctas_per_sm(const char* name, int block);
 
 /* ---- barriers -------------------------------------------------------- */
 typedef struct tccl_barrier_args {

@@ -44,12 +44,15 @@ _AR_KERNELS = {
 class Plan:
     """A bound launch.  ``run(out)``: ``out`` None → use/allocate the planned output."""
 
-    __slots__ = ("go", "args", "world", "result", "alloc", "post")
+    __slots__ = ("go", "args", "world", "result", "alloc", "post", "custom")
 
-    def __init__(self, world, go, args, result=None, alloc=None, post=None):
+    def __init__(self, world, go, args, result=None, alloc=None, post=None, custom=None):
         self.world, self.go, self.args, self.result, self.alloc, self.post = world, go, args, result, alloc, post
+        self.custom = custom  # a complete replacement of run(), for plans that do not fit the pattern
 
     def run(self):
+        if self.custom is not None:
+            return self.custom()
         if self.alloc is not None:  # fresh local output(s) per call
             outs = {}
             for r, a in self.args.items():
@@ -211,6 +214,9 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
     out_is_sym = out is not None and _is_symmetric(w, out)
     sym_dst = inplace or out_is_sym
     if algo == "auto":
+        if (not sym_dst and w.world_size > 1 and w.config.staged_twoshot and nbytes > w.config.oneshot_max_bytes
+                and nbytes <= w.config.staged_max_bytes):
+            return _plan_staged_twoshot(w, x, out, sync_exit)
         algo = choose_all_reduce_algo(w, nbytes, sym_dst)
         if algo.startswith("push"):  # not eligible after all (alignment): fall back to the pull one-shot
             algo = "oneshot_nvls" if w.has_nvls and w.world_size > 2 else "oneshot_p2p"
@@ -267,6 +273,37 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
     else:
         grid = grid_for(w, per_slice, block, 2 if w.world_size >= 8 else 4)
     return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt), args, result=dst)
+
+
+def _plan_staged_twoshot(w, x, out, sync_exit) -> Plan:
+    """Large message, ordinary destination: a one-shot kernel would pull (W-1) S into every
+    GPU.  Reduce with the two-shot kernel into a cached symmetric buffer instead and copy the
+    result out locally (one extra pass over HBM, far cheaper than W/2 times the link traffic)."""
+    x0 = w.local(x, w.local_ranks[0])
+    cache = w.__dict__.setdefault("_staged_ar", {})
+    key = (x0.numel(), x0.dtype)
+    buf = cache.get(key)
+    if buf is None:
+        buf = cache[key] = w.empty(x0.numel(), x0.dtype)
+    inner = _plan_all_reduce(w, x, buf, False, choose_all_reduce_algo(w, x0.numel() * x0.element_size(), True), sync_exit)
+    if out is not None:
+        for r in w.local_ranks:
+            _check_out(w.local(out, r), w.local(x, r))
+
+        def post():
+            for r in w.local_ranks:
+                w.local(out, r).view(-1).copy_(w.local(buf, r))
+
+        return Plan(w, inner.go, inner.args, result=out, post=post)
+
+    def run_fresh():  # a new output tensor per call, filled from the symmetric buffer
+        inner.go()
+        outs = {r: torch.empty_like(w.local(x, r)) for r in w.local_ranks}
+        for r, o in outs.items():
+            o.view(-1).copy_(w.local(buf, r))
+        return w.wrap(outs)
+
+    return Plan(w, inner.go, inner.args, custom=run_fresh)
 
 
 def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = None, sync_exit: bool = True):

@@ -198,6 +198,22 @@ def main():
         return ok
     case("allreduce/tree", tree)
 
+    def auto_paths():
+        """`algo="auto"` end to end: push (small), one-shot (medium), staged two-shot (large, ordinary
+        destination), in-place two-shot (large, symmetric)."""
+        ok = True
+        for n in (1024, 1 << 17, (1 << 22) + 8):
+            xs = [seeded(n, torch.bfloat16, 2000 + r) for r in range(W)]
+            ref = torch.stack([x.float() for x in xs]).sum(0)
+            x = w.empty(n, torch.bfloat16)
+            x.copy_(xs[rank])
+            out = tccl.all_reduce(x)
+            ok = ok and close(out, ref, torch.bfloat16, W, 2.0) and torch.equal(x.cpu(), xs[rank])
+            tccl.all_reduce(x, inplace=True)
+            ok = ok and close(x, ref, torch.bfloat16, W, 2.0)
+        return ok
+    case("allreduce/auto", auto_paths)
+
     def graph_replay():
         """A captured collective replays correctly (all sync state lives on the device)."""
         n = 1 << 14

@@ -315,3 +315,24 @@ def test_all_reduce_push_small_messages(emu_worlds, W, dtype, n):
     torch.cuda.synchronize()
     for r in range(W):
         assert_close_to_sum(y[r], ref, dtype, W)
+
+
+def test_large_all_reduce_into_ordinary_memory_uses_the_staged_two_shot(emu_worlds):
+    import tccl_b200 as tccl
+
+    W, n = 4, (1 << 20) + 8
+    w = emu_worlds(W)
+    x = make_inputs(w, W, n, torch.bfloat16, 99)
+    keep = [p.clone() for p in x.parts]
+    ref = ref_sum(x)
+    before = w.launches
+    out = tccl.all_reduce(x, world=w)          # fresh output
+    out2 = [torch.empty(n, dtype=torch.bfloat16, device=w.device) for _ in range(W)]
+    from tccl_b200.parallel.emu import EmuTensor
+    tccl.all_reduce(x, out=EmuTensor(out2), world=w)
+    torch.cuda.synchronize()
+    w.check()
+    assert w.launches == before + 2
+    for r in range(W):
+        assert_close_to_sum(out[r], ref, torch.bfloat16, W)
+        assert torch.equal(out2[r], out[r]) and torch.equal(x[r], keep[r])
