@@ -3,7 +3,7 @@ the same harness: warm-up per size, CUDA events per iteration, p50 of the
 per-iteration maximum over ranks.
 
     python -m torch.distributed.run --nproc-per-node 8 bench/sweep.py \
-        --collective allreduce,allgather,reducescatter,barrier --out gpurun_out/sweep8.jsonl
+        --collective allreduce,allgather,reducescatter,barrier --out results/sweep8.jsonl
 
 Bus bandwidth uses the nccl-tests factors: all-reduce 2 (W-1)/W on the message
 size; all-gather and reduce-scatter (W-1)/W on the total (W shards) size.

@@ -10,7 +10,7 @@ GPUs.  Activations N(0,1), weights N(0,0.02), seed 4000 + rank.  Timing: CUDA
 events per iteration, p50 of the per-iteration maximum over ranks.  Roofline =
 the slower of FLOPs / measured GEMM peak and NVLink bytes / link bandwidth.
 
-    python -m torch.distributed.run --nproc-per-node 8 bench/tp_fused.py --out gpurun_out/tp8.jsonl
+    python -m torch.distributed.run --nproc-per-node 8 bench/tp_fused.py --out results/tp8.jsonl
 """
 import argparse
 import json

@@ -7,7 +7,7 @@
  *   - a process that has already handed (nearly) all device memory to a
  *     framework's caching allocator or to a preallocating runtime, so that a
  *     direct cudaMalloc would fail;
- *   - a plug-in running inside a host application with a fixed memory budget;
+ *   - a plug-in running inside a host application whose memory is all spoken for;
  *   - a latency-critical loop that must not pay cudaMalloc's implicit
  *     device-wide synchronisation.
  *
