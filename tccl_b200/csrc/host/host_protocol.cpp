@@ -211,3 +211,89 @@ int hp_tree_allreduce(const hp_comm* h, const hp_tree* t, const hp_faults* f) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// In-process self-test: `world` ranks as threads of one process.  Built with
+// -fsanitize=thread this checks that every plain (non-atomic) access of the data
+// buffers is ordered by the release/acquire flag protocol — the race detector the
+// GPU side cannot have.  Returns 0 on success, a positive code otherwise.
+extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds) {
+  if (world < 1 || world > TCCL_MAX_WORLD) return 100;
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> data(world, std::vector<float>(numel));
+  for (int r = 0; r < world; ++r)
+    for (int i = 0; i < numel; ++i) data[r][i] = (float)((r + 1) * ((i % 7) + 1));
+  // neighbours: the same low-bit rule as parallel/tree.py
+  auto nbr_a = [&](int N, int r, int* parent, int* left, int* right) {
+    *parent = *left = *right = -1;
+    if (N == 1) return;
+    if (r == 0) {
+      int top = 1;
+      while (top * 2 <= N - 1) top *= 2;
+      *left = top;
+      return;
+    }
+    const int s = r & -r;
+    int up = (r ^ s) | (s << 1);
+    if (up >= N) up = r ^ s;
+    *parent = up;
+    if (s == 1) return;
+    *left = r - (s >> 1);
+    int step = s >> 1, rt = r + step;
+    while (rt >= N && step > 1) {
+      step >>= 1;
+      rt = r + step;
+    }
+    *right = rt >= N ? -1 : rt;
+  };
+  auto nbr = [&](int N, int r, int tree, int* parent, int* left, int* right) {
+    if (tree == 0) return nbr_a(N, r, parent, left, right);
+    nbr_a(N, (r + 1) % N, parent, left, right);
+    auto back = [&](int x) { return x < 0 ? -1 : (x - 1 + N) % N; };
+    *parent = back(*parent);
+    *left = back(*left);
+    *right = back(*right);
+  };
+  std::vector<int> results(world, 0);
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < world; ++r) {
+    ranks.emplace_back([&, r] {
+      hp_comm h{};
+      h.world = world;
+      h.rank = r;
+      for (int p = 0; p < world; ++p) h.flags[p] = reinterpret_cast<uint64_t>(flags[p].data());
+      h.local = reinterpret_cast<uint64_t>(local[r].data());
+      h.timeout_ns = 20ull * 1000 * 1000 * 1000;
+      hp_faults none{-1, 0, -1};
+      int ok = hp_barrier(&h, 1, rounds, &none);
+      hp_tree t{};
+      for (int p = 0; p < world; ++p) t.buf[p] = reinterpret_cast<uint64_t>(data[p].data());
+      t.numel = (uint64_t)numel;
+      t.chunk = (uint64_t)chunk;
+      for (int tr = 0; tr < 2; ++tr) {
+        int parent, left, right;
+        nbr(world, r, tr, &parent, &left, &right);
+        t.parent[tr] = parent;
+        t.left[tr] = left;
+        t.right[tr] = right;
+        t.child_slot[tr] = 0;
+        if (parent >= 0) {
+          int pp, pl, pr;
+          nbr(world, parent, tr, &pp, &pl, &pr);
+          t.child_slot[tr] = pl == r ? 0 : 1;
+        }
+      }
+      ok = ok && hp_tree_allreduce(&h, &t, &none);
+      results[r] = ok;
+    });
+  }
+  for (auto& th : ranks) th.join();
+  for (int r = 0; r < world; ++r)
+    if (!results[r]) return 1;
+  const float tot = (float)(world * (world + 1) / 2);
+  for (int r = 0; r < world; ++r)
+    for (int i = 0; i < numel; ++i)
+      if (data[r][i] != tot * (float)((i % 7) + 1)) return 2;
+  return 0;
+}

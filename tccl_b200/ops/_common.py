@@ -25,6 +25,16 @@ def get_world(world: Optional[WorldBase] = None) -> WorldBase:
     return w
 
 
+def debug_log(world: WorldBase, msg: str) -> None:
+    """One line per *planned* launch (plans are cached, so this is not on the hot path) when
+    ``TCCL_DEBUG=1``: which kernel, grid and block were chosen for which message."""
+    if world.config.debug:
+        import sys
+
+        rank = getattr(world, "rank", "emu")
+        print(f"[tccl_b200 rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+
 def dtype_code(dtype: torch.dtype) -> int:
     try:
         return L.DTYPES[dtype]

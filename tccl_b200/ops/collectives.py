@@ -23,7 +23,7 @@ import torch
 
 from ..parallel.world import WorldBase
 from ..utils import lib as L
-from ._common import K, check_sym_tensor, dtype_code, get_world, grid_for
+from ._common import K, check_sym_tensor, debug_log, dtype_code, get_world, grid_for
 
 __all__ = [
     "all_reduce", "all_gather", "reduce_scatter",
@@ -184,6 +184,7 @@ def _plan_push(w, x, out, inplace, algo) -> Plan:
     nvec = nbytes // 16
     block = 256 if nvec <= 2048 else 512
     grid = grid_for(w, nvec, block, 2, cap=32)
+    debug_log(w, f"all_reduce {nbytes} B -> {algo}, grid {grid} x {block}")
     go = w.prepare(_AR_KERNELS[algo], args, grid, block, dt)
     if inplace:
         for r, a in args.items():
@@ -232,6 +233,7 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
     if algo.startswith("oneshot"):
         args = {r: _copy_args(base) for r in w.local_ranks}
         grid = grid_for(w, nvec, block, 4)
+        debug_log(w, f"all_reduce {nbytes} B -> {algo}, grid {grid} x {block}")
         go = w.prepare(_AR_KERNELS[algo], args, grid, block, dt)
         if inplace:
             # a one-shot result cannot land in the buffer peers are still reading: stage it
@@ -272,6 +274,7 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
         grid = grid_for(w, per_slice, block, 8, cap=cap)
     else:
         grid = grid_for(w, per_slice, block, 2 if w.world_size >= 8 else 4)
+    debug_log(w, f"all_reduce {nbytes} B -> {algo}, grid {grid} x {block}")
     return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt), args, result=dst)
 
 

@@ -100,7 +100,7 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
     """Compile the host-side protocol model (csrc/host/*.cpp, plain g++, no CUDA)."""
     LIBDIR.mkdir(exist_ok=True)
     BUILD.mkdir(exist_ok=True)
-    srcs = sorted((CSRC / "host").glob("*.cpp"))
+    srcs = [CSRC / "host" / "host_protocol.cpp"]
     stamp = BUILD / "hostproto.sha"
     dig = _digest(srcs + headers(), "g++ -O2 -std=c++17")
     if force or not HOST_LIB.exists() or not stamp.exists() or stamp.read_text() != dig:
@@ -116,6 +116,33 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
         if verbose:
             print(f"[tccl_b200.build] built {HOST_LIB}", file=sys.stderr)
     return HOST_LIB
+
+
+def build_host_tsan(verbose: bool = False) -> Path:
+    """The protocol self-test as a ThreadSanitizer-instrumented executable."""
+    BUILD.mkdir(exist_ok=True)
+    exe = BUILD / "hostproto_tsan"
+    srcs = [CSRC / "host" / "host_protocol.cpp", CSRC / "host" / "selftest_main.cpp"]
+    stamp = BUILD / "hostproto_tsan.sha"
+    dig = _digest(srcs + headers(), "tsan")
+    if not exe.exists() or not stamp.exists() or stamp.read_text() != dig:
+        # not every toolchain ships libtsan: try the system compiler first, then $CXX
+        errors = []
+        for cxx in dict.fromkeys([shutil.which("g++", path="/usr/bin:/bin"), shutil.which("g++"), os.environ.get("CXX")]):
+            if not cxx:
+                continue
+            cmd = [cxx, "-O1", "-g", "-std=c++17", "-fsanitize=thread", "-pthread", "-I", str(CSRC), "-o", str(exe),
+                   *map(str, srcs)]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode == 0:
+                break
+            errors.append(f"{cxx}: {r.stderr.strip()[-300:]}")
+        else:
+            raise RuntimeError("g++ -fsanitize=thread failed:\n" + "\n".join(errors))
+        stamp.write_text(dig)
+        if verbose:
+            print(f"[tccl_b200.build] built {exe}", file=sys.stderr)
+    return exe
 
 
 if __name__ == "__main__":

@@ -64,3 +64,21 @@ def test_rank_that_stops_mid_all_reduce():
     assert failed, res
     wheres = {res[r]["status"]["where"] for r in failed if res[r]["status"]["code"]}
     assert wheres & {"TCCL_W_TREE_UP", "TCCL_W_TREE_DOWN", "TCCL_W_BARRIER"}
+
+
+@pytest.mark.parametrize("W", [2, 3, 4, 8])
+def test_protocol_is_race_free_under_thread_sanitizer(W):
+    """Ranks as threads of one process, instrumented with ThreadSanitizer: every plain access
+    of the data buffers must be ordered by the release/acquire flags."""
+    import subprocess
+
+    from tccl_b200.utils import build as B
+
+    try:
+        exe = B.build_host_tsan()
+    except RuntimeError as e:  # no libtsan on this machine
+        pytest.skip(str(e)[:200])
+    r = subprocess.run([str(exe), str(W), str(1 << 13), str(1 << 8)], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert "ThreadSanitizer" not in out, out[-3000:]
+    assert r.returncode == 0, out[-2000:]
