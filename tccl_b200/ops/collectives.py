@@ -107,15 +107,15 @@ def _check_out(o: torch.Tensor, like: torch.Tensor, numel: Optional[int] = None)
 
 
 def _is_symmetric(w: WorldBase, t) -> bool:
+    """Whether ``t`` is known to live in symmetric memory: allocated by ``world.empty`` or
+    resolved before (``world.handle(t)`` registers a tensor from ``symm_mem.empty``).  An
+    unknown tensor is treated as ordinary memory rather than probed with a rendezvous."""
     from ..parallel.emu import EmuTensor
 
     if isinstance(t, EmuTensor):
         return True
-    try:
-        w.peer_ptrs(t)
-        return True
-    except Exception:
-        return False
+    handles = getattr(w, "_handles", None)
+    return handles is not None and t.untyped_storage().data_ptr() in handles
 
 
 def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -> str:
