@@ -1,0 +1,80 @@
+"""Host-side decision logic that needs no GPU: kernel choice by message size and world,
+grid sizing, tree chunking, weight packing."""
+import torch
+
+from tccl_b200.config import Config
+from tccl_b200.ops._common import grid_for
+from tccl_b200.ops.collectives import choose_all_reduce_algo
+from tccl_b200.ops.fused import pack_gate_up
+from tccl_b200.ops.tree_allreduce import _tree_grid
+from tccl_b200.utils.consts import K
+
+
+class StubWorld:
+    """The few attributes the selection code reads from a communicator."""
+
+    def __init__(self, world_size, nvls, sms=148, **cfg):
+        self.world_size, self.has_nvls, self._sms = world_size, nvls, sms
+        self.config = Config()
+        for k, v in cfg.items():
+            setattr(self.config, k, v)
+        self.ll_bytes = 2 << 20
+
+    def num_sms(self):
+        return self._sms
+
+    def max_ctas(self):
+        return max(1, min(self.config.max_ctas or self._sms, K["TCCL_MAX_BLOCKS"]))
+
+    def local_copy_ctas(self):
+        return min(4 * self.max_ctas(), K["TCCL_MAX_BLOCKS"])
+
+
+def test_all_reduce_choice_follows_size_and_world():
+    w8 = StubWorld(8, True)
+    assert choose_all_reduce_algo(w8, 4096, True) == "push_nvls"
+    assert choose_all_reduce_algo(w8, 64 * 1024, False) == "push_nvls"
+    assert choose_all_reduce_algo(w8, 256 * 1024, True) == "oneshot_nvls"
+    assert choose_all_reduce_algo(w8, 16 << 20, True) == "twoshot_nvls"
+    assert choose_all_reduce_algo(w8, 16 << 20, False).startswith("oneshot")  # no symmetric destination
+    assert choose_all_reduce_algo(w8, 4100, True) == "oneshot_nvls"           # not a multiple of 16 bytes: no push
+    w2 = StubWorld(2, True)  # two ranks: NVLS moves more bytes than P2P
+    assert choose_all_reduce_algo(w2, 4096, True) == "push_p2p"
+    assert choose_all_reduce_algo(w2, 64 << 20, True) == "twoshot_p2p"
+    w4 = StubWorld(4, False)
+    assert choose_all_reduce_algo(w4, 64 << 20, True) == "twoshot_p2p"
+    assert choose_all_reduce_algo(StubWorld(1, False), 1 << 30, True) == "oneshot_p2p"
+    forced = StubWorld(8, True, force_variant="twoshot_p2p")
+    assert choose_all_reduce_algo(forced, 8, True) == "twoshot_p2p"
+
+
+def test_grid_is_a_function_of_size_and_shared_config_only():
+    w = StubWorld(8, True)
+    assert grid_for(w, 1, 512, 4) == 1
+    assert grid_for(w, 512 * 4 * 3 + 1, 512, 4) == 4
+    assert grid_for(w, 1 << 30, 512, 4) == 148
+    assert grid_for(w, 1 << 30, 512, 8, cap=8) == 8
+    assert grid_for(StubWorld(8, True, max_ctas=32), 1 << 30, 512, 4) == 32
+    assert grid_for(StubWorld(1, False), 1 << 30, 512, 8) == 592  # one rank: a local copy, several CTAs per SM
+
+
+def test_tree_grid_keeps_chunks_large_enough():
+    w = StubWorld(8, True)
+    k, vecs = _tree_grid(w, 1 << 30)
+    assert k == 32 and vecs * 16 == 4 << 20
+    k, vecs = _tree_grid(w, 1 << 20)
+    assert k == 8 and vecs * 16 >= k * 65536
+    k, vecs = _tree_grid(w, 4096)
+    assert k == 1 and vecs >= 1
+    small = StubWorld(8, True, tree_chunk_bytes=1024)
+    assert _tree_grid(small, 1 << 20)[1] == 64  # small chunks on request
+
+
+def test_pack_gate_up_layout():
+    F, Kd = 256, 8
+    gate = torch.arange(F * Kd, dtype=torch.float32).view(F, Kd)
+    up = -gate
+    p = pack_gate_up(gate, up)
+    assert p.shape == (2 * F, Kd)
+    assert torch.equal(p[:128], gate[:128]) and torch.equal(p[128:256], up[:128])
+    assert torch.equal(p[256:384], gate[128:]) and torch.equal(p[384:], up[128:])
