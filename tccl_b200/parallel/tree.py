@@ -132,3 +132,33 @@ def tree_depths(N: int, tree: int) -> List[int]:
                 raise RuntimeError("cycle in tree")
         depth[r] = d
     return depth
+
+
+def _self_test() -> None:
+    """The reference's own check (``tree.py:151-245``): literal trees and neighbour tuples."""
+    assert build_double_tree(8) == ([0, 4, 2, 6, 1, 3, 5, 7], [7, 3, 1, 5, 0, 2, 4, 6])
+    assert build_double_tree(4) == ([0, 2, 1, 3], [3, 1, 0, 2])
+    expect8 = [(-1, 4, -1, 1, -1, -1), (2, -1, -1, 3, 0, 2), (4, 1, 3, 1, -1, -1), (2, -1, -1, 7, 1, 5),
+               (0, 2, 6, 5, -1, -1), (6, -1, -1, 3, 4, 6), (4, 5, 7, 5, -1, -1), (6, -1, -1, -1, 3, -1)]
+    for r, e in enumerate(expect8):
+        assert get_parents_and_children(8, r) == e, (r, get_parents_and_children(8, r))
+    a, b = build_double_tree(32)
+    assert a[:8] == [0, 16, 8, 24, 4, 12, 20, 28] and b[:8] == [31, 15, 7, 23, 3, 11, 19, 27]
+    assert get_parents_and_children(32, 15) == (14, -1, -1, 31, 7, 23)
+    for n in range(1, 65):  # any world size: two spanning trees
+        for t in (0, 1):
+            assert sum(1 for r in range(n) if tree_neighbours(n, r, t)[0] < 0) == 1
+            tree_depths(n, t)
+
+
+if __name__ == "__main__":
+    import sys
+
+    _self_test()
+    n = int(sys.argv[1]) if len(sys.argv) > 1 else 8
+    if _is_pow2(n):
+        ta, tb = build_double_tree(n)
+        print(f"tree A: {ta}\ntree B: {tb}")
+    for r in range(n):
+        print(f"rank {r}: {get_parents_and_children(n, r)}")
+    print("All passed!")
