@@ -297,3 +297,212 @@ extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds) 
       if (data[r][i] != tot * (float)((i % 7) + 1)) return 2;
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Model of the fused GEMM -> reduce-scatter flag protocol (gemm_rs.cu), ranks and
+// CTAs as threads: entry barrier per CTA index; every "CTA" walks its tiles in owner
+// order (own rows first), writes a partial into slot [src][tile] of the OWNER's
+// staging area with plain stores and raises that tile's epoch flag one tile later
+// (the deferred release of the copy-engine epilogue); the final phase shares the
+// rank's tiles out over all CTAs, acquires the W flags of a tile and sums the slots;
+// the last CTA of a rank to finish advances the epoch.  Two calls run back to back
+// so that slot reuse across calls (protected by the entry barrier) is covered too.
+// Under ThreadSanitizer this verifies that every plain slot access is ordered.
+extern "C" int hp_selftest_gemm_rs(int world, int ctas, int tiles_per_owner, int calls) {
+  if (world < 1 || world > TCCL_MAX_WORLD || ctas < 1 || ctas > 64 || tiles_per_owner > 64) return 100;
+  constexpr int kElems = 16;  // one "tile" of the model
+  const int tpo = tiles_per_owner;
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> stage(world, std::vector<float>((size_t)world * tpo * kElems, 0.f));
+  std::vector<std::vector<float>> out(world, std::vector<float>((size_t)tpo * kElems, 0.f));
+  std::atomic<int> bad{0};
+  auto partial = [](int call, int src, int owner, int lt, int e) {
+    return (float)((call + 1) * 1000 + src * 100 + owner * 10 + lt) + 0.25f * e;
+  };
+  for (int call = 0; call < calls; ++call) {
+    std::vector<std::thread> th;
+    for (int r = 0; r < world; ++r)
+      for (int b = 0; b < ctas; ++b)
+        th.emplace_back([&, r, b, call] {
+          HostComm c;
+          c.world = world;
+          c.rank = r;
+          for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+          c.local = local[r].data();
+          c.timeout_ns = 20ull * 1000 * 1000 * 1000;
+          const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+          Faults none{-1, 0, -1};
+          const uint32_t epoch = A(c.local + TCCL_LOCAL_TILE_EPOCH).load(std::memory_order_relaxed) + 1u;
+          // per-CTA barrier row: the model keeps one epoch word per (rank, bid) like the device
+          {
+            // barrier() updates c.local[EPOCH + bid]; rows are private to this CTA index
+            if (!barrier(c, b, deadline, none)) bad.store(1);
+          }
+          uint32_t* pending = nullptr;
+          for (int t = b; t < world * tpo; t += ctas) {
+            const int j = t / tpo, lt = t - j * tpo;
+            const int owner = (r + j) % world;
+            if (pending) {  // flush the previous tile's flag (its "copies" are complete)
+              A(pending).store(epoch, std::memory_order_release);
+              pending = nullptr;
+            }
+            float* slot = stage[owner].data() + ((size_t)r * tpo + lt) * kElems;
+            for (int e = 0; e < kElems; ++e) slot[e] = partial(call, r, owner, lt, e);
+            pending = c.flags[owner] + TCCL_FLAG_TILE + r * TCCL_MAX_TILES + lt;
+          }
+          if (pending) A(pending).store(epoch, std::memory_order_release);
+          // final phase: tiles of this rank shared out over its CTAs
+          for (int lt = b; lt < tpo; lt += ctas) {
+            bool ok = true;
+            for (int src = 0; src < world && ok; ++src)
+              ok = wait_reach(c.flags[r] + TCCL_FLAG_TILE + src * TCCL_MAX_TILES + lt, epoch, c, deadline, b, src,
+                              TCCL_W_TILE);
+            if (!ok) {
+              bad.store(2);
+              return;
+            }
+            for (int e = 0; e < kElems; ++e) {
+              float s = 0.f;
+              for (int src = 0; src < world; ++src) s += stage[r][((size_t)src * tpo + lt) * kElems + e];
+              out[r][(size_t)lt * kElems + e] = s;
+            }
+          }
+          // the last CTA of the rank publishes the epoch for the next call
+          const uint32_t done = A(c.local + TCCL_LOCAL_SCHED).fetch_add(1u, std::memory_order_acq_rel);
+          if (done == (uint32_t)ctas - 1u) {
+            A(c.local + TCCL_LOCAL_SCHED).store(0u, std::memory_order_relaxed);
+            A(c.local + TCCL_LOCAL_TILE_EPOCH).store(epoch, std::memory_order_release);
+          }
+        });
+    for (auto& x : th) x.join();  // = stream order: a rank's next kernel starts after this one ended
+    if (bad.load()) return bad.load();
+    for (int r = 0; r < world; ++r)
+      for (int lt = 0; lt < tpo; ++lt)
+        for (int e = 0; e < kElems; ++e) {
+          float s = 0.f;
+          for (int src = 0; src < world; ++src) s += partial(call, src, r, lt, e);
+          if (out[r][(size_t)lt * kElems + e] != s) return 3;
+        }
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Model of the all-gather -> GEMM arrival protocol (ag_gemm.cu): `movers` threads per
+// rank copy their share of every row tile of the rank's shard into slot [rank] of every
+// rank's gathered buffer (plain stores), count themselves done per row tile, and the
+// last one raises the row tile's epoch flag on every rank; `consumers` threads per rank
+// wait for a remote row tile's flag before reading its rows.  Movers start with their
+// own barrier row (the previous call's readers are done); the last thread of a rank to
+// finish advances the epoch.
+extern "C" int hp_selftest_ag(int world, int movers, int consumers, int row_tiles, int calls) {
+  if (world < 1 || world > TCCL_MAX_WORLD || movers < 1 || movers > 32 || consumers < 1 || consumers > 32) return 100;
+  constexpr int kRow = 24;  // elements per row tile in the model
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> full(world, std::vector<float>((size_t)world * row_tiles * kRow, 0.f));
+  std::atomic<int> bad{0};
+  auto val = [](int call, int src, int rt, int e) { return (float)(call * 10000 + src * 1000 + rt * 50 + e); };
+  const int nthreads = movers + consumers;
+  for (int call = 0; call < calls; ++call) {
+    std::vector<std::thread> th;
+    for (int r = 0; r < world; ++r)
+      for (int b = 0; b < nthreads; ++b)
+        th.emplace_back([&, r, b, call] {
+          HostComm c;
+          c.world = world;
+          c.rank = r;
+          for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+          c.local = local[r].data();
+          c.timeout_ns = 20ull * 1000 * 1000 * 1000;
+          const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+          Faults none{-1, 0, -1};
+          const uint32_t epoch = A(c.local + TCCL_LOCAL_TILE_EPOCH).load(std::memory_order_relaxed) + 1u;
+          if (b < movers) {
+            if (!barrier(c, b, deadline, none)) bad.store(1);
+            for (int rt = 0; rt < row_tiles; ++rt) {
+              for (int e = b; e < kRow; e += movers)
+                for (int q = 0; q < world; ++q) full[q][((size_t)r * row_tiles + rt) * kRow + e] = val(call, r, rt, e);
+              const uint32_t done = A(c.local + TCCL_LOCAL_AGCNT + rt).fetch_add(1u, std::memory_order_acq_rel);
+              if (done == (uint32_t)movers - 1u) {
+                A(c.local + TCCL_LOCAL_AGCNT + rt).store(0u, std::memory_order_relaxed);
+                for (int q = 0; q < world; ++q)
+                  A(c.flags[q] + TCCL_FLAG_AG + r * TCCL_MAX_ROW_TILES + rt).store(epoch, std::memory_order_release);
+              }
+            }
+          } else {
+            const int cb = b - movers;
+            for (int t = cb; t < world * row_tiles; t += consumers) {
+              const int src = t / row_tiles, rt = t - src * row_tiles;
+              if (src != r &&
+                  !wait_reach(c.flags[r] + TCCL_FLAG_AG + src * TCCL_MAX_ROW_TILES + rt, epoch, c, deadline, b, src,
+                              TCCL_W_TILE)) {
+                bad.store(2);
+                return;
+              }
+              if (src == r) continue;  // own rows come straight from the shard
+              for (int e = 0; e < kRow; ++e)
+                if (full[r][((size_t)src * row_tiles + rt) * kRow + e] != val(call, src, rt, e)) bad.store(3);
+            }
+          }
+          const uint32_t done = A(c.local + TCCL_LOCAL_SCHED).fetch_add(1u, std::memory_order_acq_rel);
+          if (done == (uint32_t)nthreads - 1u) {
+            A(c.local + TCCL_LOCAL_SCHED).store(0u, std::memory_order_relaxed);
+            A(c.local + TCCL_LOCAL_TILE_EPOCH).store(epoch, std::memory_order_release);
+          }
+        });
+    for (auto& x : th) x.join();
+    if (bad.load()) return bad.load();
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Model of the small-message push all-reduce (AllReduceOneShotPush): every rank stores its
+// input into slot [parity][rank] of every rank, ONE barrier, local sum — and no exit
+// barrier: the slot parity (low bit of the barrier epoch) alternates from call to call.
+// Ranks run free of each other between calls (each rank is one thread looping over the
+// calls), so a rank may be a call ahead of a peer; ThreadSanitizer checks that the slot
+// being overwritten is never still being read.
+extern "C" int hp_selftest_push(int world, int calls) {
+  if (world < 1 || world > TCCL_MAX_WORLD) return 100;
+  constexpr int kElems = 32;
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> slots(world, std::vector<float>((size_t)2 * world * kElems, 0.f));
+  std::atomic<int> bad{0};
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    th.emplace_back([&, r] {
+      HostComm c;
+      c.world = world;
+      c.rank = r;
+      for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+      c.local = local[r].data();
+      c.timeout_ns = 20ull * 1000 * 1000 * 1000;
+      Faults none{-1, 0, -1};
+      for (int call = 0; call < calls; ++call) {
+        const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+        const uint32_t e = c.local[TCCL_LOCAL_EPOCH + 0] + 1u;
+        const size_t base = (size_t)(e & 1u) * world * kElems;
+        for (int q = 0; q < world; ++q)
+          for (int i = 0; i < kElems; ++i) slots[q][base + (size_t)r * kElems + i] = (float)(call * 100 + r * 10 + i % 3);
+        if (!barrier(c, 0, deadline, none)) {
+          bad.store(1);
+          return;
+        }
+        for (int i = 0; i < kElems; ++i) {
+          float s = 0.f, want = 0.f;
+          for (int p = 0; p < world; ++p) {
+            s += slots[r][base + (size_t)p * kElems + i];
+            want += (float)(call * 100 + p * 10 + i % 3);
+          }
+          if (s != want) bad.store(2);
+        }
+        if ((call & 3) == r % 4) std::this_thread::yield();  // let the ranks drift apart
+      }
+    });
+  for (auto& x : th) x.join();
+  return bad.load();
+}

@@ -68,8 +68,10 @@ def test_rank_that_stops_mid_all_reduce():
 
 @pytest.mark.parametrize("W", [2, 3, 4, 8])
 def test_protocol_is_race_free_under_thread_sanitizer(W):
-    """Ranks as threads of one process, instrumented with ThreadSanitizer: every plain access
-    of the data buffers must be ordered by the release/acquire flags."""
+    """Ranks (and CTAs) as threads of one process, instrumented with ThreadSanitizer: every plain
+    access of the data buffers must be ordered by the release/acquire flags.  Covers the barrier,
+    the double-tree pipeline, the GEMM -> reduce-scatter tile flags (deferred release, final phase,
+    epoch hand-over across calls) and the all-gather -> GEMM arrival flags."""
     import subprocess
 
     from tccl_b200.utils import build as B
