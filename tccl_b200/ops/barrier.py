@@ -11,8 +11,6 @@ from __future__ import annotations
 
 from typing import Optional
 
-import torch
-
 from ..parallel.world import WorldBase
 from ..utils import lib as L
 from ._common import K, get_world

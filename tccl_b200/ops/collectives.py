@@ -17,13 +17,13 @@ call.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Callable, Dict, Optional
+from typing import Callable, Optional
 
 import torch
 
 from ..parallel.world import WorldBase
 from ..utils import lib as L
-from ._common import K, check_sym_tensor, debug_log, dtype_code, get_world, grid_for
+from ._common import check_sym_tensor, debug_log, dtype_code, get_world, grid_for
 
 __all__ = [
     "all_reduce", "all_gather", "reduce_scatter",

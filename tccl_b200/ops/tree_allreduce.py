@@ -17,8 +17,6 @@ from __future__ import annotations
 
 from typing import Optional
 
-import torch
-
 from ..parallel.tree import tree_neighbours
 from ..parallel.world import WorldBase
 from ..utils import lib as L

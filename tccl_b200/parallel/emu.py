@@ -12,7 +12,7 @@ A symmetric tensor is an ``EmuTensor``: a list-like of W per-rank tensors.
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, List, Optional
+from typing import List, Optional
 
 import torch
 

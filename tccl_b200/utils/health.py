@@ -16,7 +16,7 @@ timeouts: ``triton_barrier.py:108-118``).
 from __future__ import annotations
 
 import time
-from typing import Dict, List, Optional
+from typing import Dict, List
 
 
 class PeerLost(RuntimeError):

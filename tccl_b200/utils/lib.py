@@ -8,9 +8,7 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-import re
 from pathlib import Path
-from typing import Dict
 
 import torch
 
@@ -18,7 +16,7 @@ PKG = Path(__file__).resolve().parent.parent
 LIB_PATH = PKG / "_lib" / "libtccl_b200.so"
 
 
-from .consts import HEADER, K, MAX_WORLD  # noqa: E402,F401  (parsed from csrc/tccl_b200.h)
+from .consts import K, MAX_WORLD  # noqa: E402,F401  (parsed from csrc/tccl_b200.h)
 
 
 class Comm(C.Structure):

@@ -1,6 +1,5 @@
 """Host-side checks that need no GPU: header constants, struct sizes, config."""
 import ctypes as C
-import os
 
 from tccl_b200.config import Config
 from tccl_b200.utils import lib as L

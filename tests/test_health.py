@@ -6,7 +6,6 @@ import datetime
 import os
 import time
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
