@@ -40,6 +40,7 @@ class Config:
     tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
+    plan_cache_size: int = 512            # bound launches kept per communicator (least recently used go first)
     debug: bool = False
 
     @classmethod

@@ -209,16 +209,26 @@ struct AllReduceOneShotNvls {
 
 // --------------------------------------------- one-shot all-reduce, push variant
 // Latency path for small messages.  Every rank stores its input into slot
-// [parity][rank] of every rank's staging area (posted stores, or one
+// [half][rank] of every rank's small-message region (posted stores, or one
 // multimem.st), then ONE barrier both publishes the data and tells everybody it
 // is there, and each rank sums the W slots out of its OWN memory.  Compared with
 // the pull variant this drops a barrier round and replaces the peer-load round
-// trip by local loads.  No exit barrier is needed: the two parities alternate
-// from call to call (the parity is the low bit of the barrier epoch), and a rank
-// can only be two calls ahead of a peer after a barrier that the peer has
-// reached, i.e. after the peer has finished reading the slot being reused.  The
-// input does not have to live in symmetric memory.
-// `out_peer[p]` / `mc_out` carry the staging region of rank p / its multicast alias.
+// trip by local loads.  The input does not have to live in symmetric memory.
+//
+// No exit barrier is needed because the two halves of the region alternate from
+// call to call.  The half is the low bit of a per-communicator count of completed
+// push calls (TCCL_LOCAL_PUSH_SEQ, advanced by the last CTA of each launch), and
+// the slot layout is fixed: half h starts at h * ll_bytes / 2 and rank r's slot at
+// r * push_slot_bytes, whatever the message size or the grid.  A rank can start
+// call n+2 (same half as call n) only after its call n+1 has completed, i.e. after
+// a barrier of call n+1 that every peer has reached, and a peer reaches call n+1
+// only after its kernel of call n, including the local sum, has finished.  So the
+// bytes being overwritten are never still being read, also when consecutive
+// calls differ in size or in grid.
+__host__ __device__ __forceinline__ uint64_t push_slot_bytes(uint64_t ll_bytes, int world) {
+  return (ll_bytes / 2 / (uint64_t)world) & ~(uint64_t)15;
+}
+
 template <typename T, int W, bool kNvls>
 struct AllReduceOneShotPush {
   using Args = tccl_coll_args;
@@ -229,12 +239,13 @@ struct AllReduceOneShotPush {
     const uint64_t deadline = globaltimer() + c.timeout_ns;
     const int world = WorldOf<W>::get(c);
     constexpr int VPT = VecOf<T>::n;
-    const uint64_t nvec = a.numel / VPT;  // the host guarantees a whole number of vectors
-    const uint64_t slot = nvec * 16;
+    const uint64_t nvec = a.numel / VPT;  // the host guarantees a whole number of vectors that fits a slot
+    const uint64_t slot = push_slot_bytes(c.ll_bytes, world);
     const uint64_t bs = blockDim.x;
     const bool nvls_bar = (a.flags & TCCL_F_NVLS_BARRIER) != 0;
-    const uint32_t e = (nvls_bar ? c.local[TCCL_LOCAL_MCEPOCH + bid] : c.local[TCCL_LOCAL_EPOCH + bid]) + 1u;
-    const uint64_t base = (uint64_t)(e & 1u) * world * slot;
+    // stable for the whole launch: only this launch's last CTA advances it, on its way out
+    const uint32_t seq = ld_relaxed_sys(c.local + TCCL_LOCAL_PUSH_SEQ);
+    const uint64_t base = c.stage_bytes + (uint64_t)(seq & 1u) * (c.ll_bytes / 2);
     const char* src = reinterpret_cast<const char*>(a.in[c.rank]);
     const uint64_t mine = base + (uint64_t)c.rank * slot;
     TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
@@ -244,17 +255,17 @@ struct AllReduceOneShotPush {
         if (i < nvec) {
           const Vec16 v = ld_peer(src + i * 16);
           if (kNvls) {
-            multimem_st(reinterpret_cast<char*>(a.mc_out) + mine + i * 16, v);
+            multimem_st(c.mc_stage + mine + i * 16, v);
           } else {
 #pragma unroll
             for (int p = 0; p < kMaxW; ++p)
-              if (p < world) st_peer(reinterpret_cast<char*>(a.out_peer[p]) + mine + i * 16, v);
+              if (p < world) st_peer(c.stage[p] + mine + i * 16, v);
           }
         }
       }
     }
     barrier_any(c, bid, deadline, nvls_bar);  // data of all ranks for this CTA's slabs has landed here
-    const char* local = reinterpret_cast<const char*>(a.out_peer[c.rank]) + base;
+    const char* local = c.stage[c.rank] + base;
     TCCL_FOR_SLABS(U, nvec, bid, nb, i0) {
       Vec16 v[kMaxW][U];
 #pragma unroll
@@ -274,6 +285,16 @@ struct AllReduceOneShotPush {
             if (p < world) acc.add(v[p][u]);
           st_local(vptr<T>(a.out, i0 + u * bs), acc.pack());
         }
+    }
+    // the last CTA of this rank to finish flips the half for the next push call
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_PUSH_DONE, 1u);
+      if (done == (uint32_t)nb - 1u) {
+        c.local[TCCL_LOCAL_PUSH_DONE] = 0u;
+        st_relaxed_sys(c.local + TCCL_LOCAL_PUSH_SEQ, seq + 1u);
+      }
     }
   }
 };
@@ -555,6 +576,10 @@ static inline void host_meta(const tccl_comm* comm, const tccl_coll_args* args, 
 }
 
 extern "C" {
+
+uint64_t tccl_push_slot_bytes(uint64_t ll_bytes, int world) {
+  return world >= 1 ? push_slot_bytes(ll_bytes, world) : 0;
+}
 
 int tccl_barrier_p2p(const tccl_comm* comm, const tccl_barrier_args* args, const tccl_launch* l) {
   return launch_op<BarrierP2POp>(comm, args, l);

@@ -90,54 +90,79 @@ uint32_t* up_flag(const HostComm& c, int rank, int tree, int k, int slot) {
 uint32_t* down_flag(const HostComm& c, int rank, int tree, int k) {
   return c.flags[rank] + TCCL_FLAG_TREE_DOWN + (tree * TCCL_TREE_MAX_CTAS + k);
 }
+uint32_t* ack_flag(const HostComm& c, int rank, int tree, int k) {
+  return c.flags[rank] + TCCL_FLAG_TREE_ACK + (tree * TCCL_TREE_MAX_CTAS + k);
+}
 
 struct TreeJob {
-  float* buf[TCCL_MAX_WORLD];
+  const float* in;              // this rank's input (read by nobody else)
+  float* buf[TCCL_MAX_WORLD];   // every rank's result buffer; parents store the sum into their children's
+  float* ring[TCCL_MAX_WORLD];  // every rank's ring: [tree][child slot][chunk % depth][chunk elements]
   uint64_t numel, chunk;
+  uint64_t ring_stride;         // elements per ring slot: fixed for the communicator, >= any chunk
   int parent[2], left[2], right[2], child_slot[2];
 };
+constexpr int kDepth = TCCL_TREE_RING_DEPTH;
 
-// one (tree, direction) worker = what one CTA does on the device (K = 1 slice)
+float* ring_slot(const TreeJob& j, int rank, int tree, int cslot, uint32_t seq) {
+  return j.ring[rank] + ((size_t)((tree * 2 + cslot) * kDepth) + seq % kDepth) * j.ring_stride;
+}
+
+// one (tree, direction) worker = what one CTA does on the device (K = 1 slice): the push
+// protocol of tree_allreduce.cu with the same counters, running totals and ring reuse rule
 void tree_worker(const HostComm& c, const TreeJob& j, int tree, bool is_up, clk::time_point deadline, const Faults& f) {
   const int me = c.rank, parent = j.parent[tree], left = j.left[tree], right = j.right[tree];
+  const int cslot = j.child_slot[tree];
   const uint64_t nchunks = (j.numel + j.chunk - 1) / j.chunk;
   const uint64_t mine = nchunks > (uint64_t)tree ? (nchunks - tree + 1) / 2 : 0;
-  float* own = j.buf[me];
+  const int role = (is_up ? 0 : 2) + tree;
+  uint32_t* seq_word = c.local + TCCL_LOCAL_TREE_SEQ + role * TCCL_TREE_MAX_CTAS;
+  const uint32_t base = *seq_word;
   if (is_up) {
-    const bool leaf = left < 0 && right < 0;
-    if (leaf) {
-      if (parent >= 0 && mine && f.stop_after_chunk != 0)
-        A(up_flag(c, parent, tree, 0, j.child_slot[tree])).store(
-            (uint32_t)(f.stop_after_chunk > 0 && (uint64_t)f.stop_after_chunk < mine ? f.stop_after_chunk : mine),
-            std::memory_order_release);
-      return;
-    }
     for (uint64_t n = 0; n < mine; ++n) {
       if (f.stop_after_chunk >= 0 && n >= (uint64_t)f.stop_after_chunk) return;  // injected: this rank stops here
-      if (!wait_reach(up_flag(c, me, tree, 0, 0), (uint32_t)(n + 1), c, deadline, tree, left, TCCL_W_TREE_UP)) return;
-      if (right >= 0 &&
-          !wait_reach(up_flag(c, me, tree, 0, 1), (uint32_t)(n + 1), c, deadline, tree, right, TCCL_W_TREE_UP))
+      const uint32_t g = base + (uint32_t)n;
+      if (left >= 0 && !wait_reach(up_flag(c, me, tree, 0, 0), g + 1u, c, deadline, tree, left, TCCL_W_TREE_UP)) return;
+      if (right >= 0 && !wait_reach(up_flag(c, me, tree, 0, 1), g + 1u, c, deadline, tree, right, TCCL_W_TREE_UP)) return;
+      if (parent >= 0 &&
+          !wait_reach(ack_flag(c, me, tree, 0), g + 1u - (uint32_t)kDepth, c, deadline, tree, parent, TCCL_W_TREE_UP))
         return;
       const uint64_t lo = (2 * n + tree) * j.chunk, hi = std::min(lo + j.chunk, j.numel);
-      for (uint64_t i = lo; i < hi; ++i) own[i] += j.buf[left][i] + (right >= 0 ? j.buf[right][i] : 0.f);
-      if (parent >= 0) {
-        A(up_flag(c, parent, tree, 0, j.child_slot[tree])).store((uint32_t)(n + 1), std::memory_order_release);
-      } else {
-        A(down_flag(c, left, tree, 0)).store((uint32_t)(n + 1), std::memory_order_release);
-        if (right >= 0) A(down_flag(c, right, tree, 0)).store((uint32_t)(n + 1), std::memory_order_release);
+      const float* lr = left >= 0 ? ring_slot(j, me, tree, 0, g) : nullptr;
+      const float* rr = right >= 0 ? ring_slot(j, me, tree, 1, g) : nullptr;
+      float* pr = parent >= 0 ? ring_slot(j, parent, tree, cslot, g) : nullptr;
+      for (uint64_t i = lo; i < hi; ++i) {
+        const float v = j.in[i] + (lr ? lr[i - lo] : 0.f) + (rr ? rr[i - lo] : 0.f);
+        if (pr) {
+          pr[i - lo] = v;
+        } else {  // the root: the final value goes to its own and its children's result buffers
+          j.buf[me][i] = v;
+          if (left >= 0) j.buf[left][i] = v;
+          if (right >= 0) j.buf[right][i] = v;
+        }
       }
+      if (parent >= 0) {
+        A(up_flag(c, parent, tree, 0, cslot)).store(g + 1u, std::memory_order_release);
+      } else {
+        if (left >= 0) A(down_flag(c, left, tree, 0)).store(g + 1u, std::memory_order_release);
+        if (right >= 0) A(down_flag(c, right, tree, 0)).store(g + 1u, std::memory_order_release);
+      }
+      if (left >= 0) A(ack_flag(c, left, tree, 0)).store(g + 1u, std::memory_order_release);
+      if (right >= 0) A(ack_flag(c, right, tree, 0)).store(g + 1u, std::memory_order_release);
     }
   } else if (parent >= 0) {
     for (uint64_t n = 0; n < mine; ++n) {
       if (f.stop_after_chunk >= 0 && n >= (uint64_t)f.stop_after_chunk) return;
-      if (!wait_reach(down_flag(c, me, tree, 0), (uint32_t)(n + 1), c, deadline, 2 + tree, parent, TCCL_W_TREE_DOWN))
-        return;
+      const uint32_t g = base + (uint32_t)n;
+      if (!wait_reach(down_flag(c, me, tree, 0), g + 1u, c, deadline, 2 + tree, parent, TCCL_W_TREE_DOWN)) return;
       const uint64_t lo = (2 * n + tree) * j.chunk, hi = std::min(lo + j.chunk, j.numel);
-      std::memcpy(own + lo, j.buf[parent] + lo, (hi - lo) * sizeof(float));
-      if (left >= 0) A(down_flag(c, left, tree, 0)).store((uint32_t)(n + 1), std::memory_order_release);
-      if (right >= 0) A(down_flag(c, right, tree, 0)).store((uint32_t)(n + 1), std::memory_order_release);
+      if (left >= 0) std::memcpy(j.buf[left] + lo, j.buf[me] + lo, (hi - lo) * sizeof(float));
+      if (right >= 0) std::memcpy(j.buf[right] + lo, j.buf[me] + lo, (hi - lo) * sizeof(float));
+      if (left >= 0) A(down_flag(c, left, tree, 0)).store(g + 1u, std::memory_order_release);
+      if (right >= 0) A(down_flag(c, right, tree, 0)).store(g + 1u, std::memory_order_release);
     }
   }
+  *seq_word = base + (uint32_t)mine;
 }
 
 }  // namespace
@@ -154,8 +179,10 @@ struct hp_faults {
   int32_t drop_signal_to, stall_ms, stop_after_chunk;
 };
 struct hp_tree {
-  uint64_t buf[TCCL_MAX_WORLD];
-  uint64_t numel, chunk;
+  uint64_t in;                    // this rank's input
+  uint64_t buf[TCCL_MAX_WORLD];   // result buffers (the inputs themselves when reducing in place)
+  uint64_t ring[TCCL_MAX_WORLD];  // 4 * TCCL_TREE_RING_DEPTH * ring_stride floats per rank
+  uint64_t numel, chunk, ring_stride;
   int32_t parent[2], left[2], right[2], child_slot[2];
 };
 
@@ -179,15 +206,21 @@ int hp_barrier(const hp_comm* h, int bid, int rounds, const hp_faults* f) {
   return 1;
 }
 
-// pipelined double-tree all-reduce in place over float buffers in shared memory
+// pipelined double-tree all-reduce over float buffers in shared memory; like the kernel it has
+// neither an entry nor an exit barrier (counters are running totals, the ring has a fixed layout)
 int hp_tree_allreduce(const hp_comm* h, const hp_tree* t, const hp_faults* f) {
   HostComm c = to_comm(h);
   Faults ft{-1, f ? f->stall_ms : 0, f ? f->stop_after_chunk : -1};
-  Faults none{-1, 0, -1};
   TreeJob j;
-  for (int p = 0; p < TCCL_MAX_WORLD; ++p) j.buf[p] = reinterpret_cast<float*>(t->buf[p]);
+  j.in = reinterpret_cast<const float*>(t->in);
+  for (int p = 0; p < TCCL_MAX_WORLD; ++p) {
+    j.buf[p] = reinterpret_cast<float*>(t->buf[p]);
+    j.ring[p] = reinterpret_cast<float*>(t->ring[p]);
+  }
   j.numel = t->numel;
   j.chunk = t->chunk;
+  j.ring_stride = t->ring_stride;
+  if (j.chunk > j.ring_stride) return 0;
   for (int i = 0; i < 2; ++i) {
     j.parent[i] = t->parent[i];
     j.left[i] = t->left[i];
@@ -195,19 +228,12 @@ int hp_tree_allreduce(const hp_comm* h, const hp_tree* t, const hp_faults* f) {
     j.child_slot[i] = t->child_slot[i];
   }
   const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
-  if (!barrier(c, 0, deadline, none)) return 0;  // buffers ready, counters zero
+  if (ft.stall_ms > 0) std::this_thread::sleep_for(std::chrono::milliseconds(ft.stall_ms));
   std::vector<std::thread> th;
   for (int tree = 0; tree < 2; ++tree)
     for (int up = 0; up < 2; ++up) th.emplace_back([&, tree, up] { tree_worker(c, j, tree, up != 0, deadline, ft); });
   for (auto& x : th) x.join();
-  // the owner zeroes the counters it consumed, then everybody leaves together
-  for (int tree = 0; tree < 2; ++tree) {
-    A(up_flag(c, c.rank, tree, 0, 0)).store(0u, std::memory_order_relaxed);
-    A(up_flag(c, c.rank, tree, 0, 1)).store(0u, std::memory_order_relaxed);
-    A(down_flag(c, c.rank, tree, 0)).store(0u, std::memory_order_relaxed);
-  }
-  const bool ok = barrier(c, 0, deadline, none);
-  return ok && !aborted(c) ? 1 : 0;
+  return !aborted(c) ? 1 : 0;
 }
 
 }  // extern "C"
@@ -219,11 +245,12 @@ int hp_tree_allreduce(const hp_comm* h, const hp_tree* t, const hp_faults* f) {
 // GPU side cannot have.  Returns 0 on success, a positive code otherwise.
 extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds) {
   if (world < 1 || world > TCCL_MAX_WORLD) return 100;
+  constexpr int kCalls = 4;  // back to back, no barrier in between, alternating chunk sizes
   std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
   std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
   std::vector<std::vector<float>> data(world, std::vector<float>(numel));
-  for (int r = 0; r < world; ++r)
-    for (int i = 0; i < numel; ++i) data[r][i] = (float)((r + 1) * ((i % 7) + 1));
+  std::vector<std::vector<float>> rings(world, std::vector<float>((size_t)4 * TCCL_TREE_RING_DEPTH * chunk, 0.f));
+  std::atomic<int> bad{0};
   // neighbours: the same low-bit rule as parallel/tree.py
   auto nbr_a = [&](int N, int r, int* parent, int* left, int* right) {
     *parent = *left = *right = -1;
@@ -267,35 +294,44 @@ extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds) 
       h.timeout_ns = 20ull * 1000 * 1000 * 1000;
       hp_faults none{-1, 0, -1};
       int ok = hp_barrier(&h, 1, rounds, &none);
-      hp_tree t{};
-      for (int p = 0; p < world; ++p) t.buf[p] = reinterpret_cast<uint64_t>(data[p].data());
-      t.numel = (uint64_t)numel;
-      t.chunk = (uint64_t)chunk;
-      for (int tr = 0; tr < 2; ++tr) {
-        int parent, left, right;
-        nbr(world, r, tr, &parent, &left, &right);
-        t.parent[tr] = parent;
-        t.left[tr] = left;
-        t.right[tr] = right;
-        t.child_slot[tr] = 0;
-        if (parent >= 0) {
-          int pp, pl, pr;
-          nbr(world, parent, tr, &pp, &pl, &pr);
-          t.child_slot[tr] = pl == r ? 0 : 1;
+      for (int call = 0; call < kCalls && ok; ++call) {
+        // this rank's own data only: written here, read by its up workers, overwritten with the
+        // sum by its parent (after this rank has contributed the chunk) — the in-place form
+        for (int i = 0; i < numel; ++i) data[r][i] = (float)((r + 1) * ((i % 7) + 1) + call);
+        hp_tree t{};
+        t.in = reinterpret_cast<uint64_t>(data[r].data());
+        for (int p = 0; p < world; ++p) {
+          t.buf[p] = reinterpret_cast<uint64_t>(data[p].data());
+          t.ring[p] = reinterpret_cast<uint64_t>(rings[p].data());
         }
+        t.numel = (uint64_t)numel;
+        t.chunk = (uint64_t)((call & 1) ? std::max(1, chunk / 2) : chunk);
+        t.ring_stride = (uint64_t)chunk;
+        for (int tr = 0; tr < 2; ++tr) {
+          int parent, left, right;
+          nbr(world, r, tr, &parent, &left, &right);
+          t.parent[tr] = parent;
+          t.left[tr] = left;
+          t.right[tr] = right;
+          t.child_slot[tr] = 0;
+          if (parent >= 0) {
+            int pp, pl, pr;
+            nbr(world, parent, tr, &pp, &pl, &pr);
+            t.child_slot[tr] = pl == r ? 0 : 1;
+          }
+        }
+        ok = ok && hp_tree_allreduce(&h, &t, &none);
+        const float tot = (float)(world * (world + 1) / 2);
+        for (int i = 0; i < numel && ok; ++i)
+          if (data[r][i] != tot * (float)((i % 7) + 1) + (float)(world * call)) bad.store(2);
       }
-      ok = ok && hp_tree_allreduce(&h, &t, &none);
       results[r] = ok;
     });
   }
   for (auto& th : ranks) th.join();
   for (int r = 0; r < world; ++r)
     if (!results[r]) return 1;
-  const float tot = (float)(world * (world + 1) / 2);
-  for (int r = 0; r < world; ++r)
-    for (int i = 0; i < numel; ++i)
-      if (data[r][i] != tot * (float)((i % 7) + 1)) return 2;
-  return 0;
+  return bad.load();
 }
 
 // ---------------------------------------------------------------------------
@@ -460,49 +496,102 @@ extern "C" int hp_selftest_ag(int world, int movers, int consumers, int row_tile
 
 // ---------------------------------------------------------------------------
 // Model of the small-message push all-reduce (AllReduceOneShotPush): every rank stores its
-// input into slot [parity][rank] of every rank, ONE barrier, local sum — and no exit
-// barrier: the slot parity (low bit of the barrier epoch) alternates from call to call.
-// Ranks run free of each other between calls (each rank is one thread looping over the
-// calls), so a rank may be a call ahead of a peer; ThreadSanitizer checks that the slot
-// being overwritten is never still being read.
-extern "C" int hp_selftest_push(int world, int calls) {
+// input into slot [half][rank] of every rank, ONE barrier, local sum, and no exit barrier.
+// A rank is `kCtas` threads (the CTAs of its launch) that meet at a kernel boundary between
+// calls, as kernels of one stream do; the ranks run free of each other, so a rank may be a
+// call ahead of a peer.  Consecutive calls differ in message size and in grid.  All slot
+// accesses are plain loads and stores: ThreadSanitizer checks that the bytes being
+// overwritten are never still being read.
+//   scheme 0 (the kernel): fixed slot layout — half h at h * region / 2, rank r's slot at
+//            r * slot_elems — and the half taken from a per-rank count of completed push calls
+//            that the last CTA of a launch advances.
+//   scheme 1 (a broken variant kept to show that the check has teeth): slot size = message size
+//            and the half = low bit of the CTA's own barrier epoch.  With mixed sizes and grids
+//            a fast rank overwrites bytes a slow peer is still summing: a data race (and often
+//            a wrong sum).
+namespace {
+struct KernelBoundary {  // sense-reversing barrier among the CTA threads of one rank
+  std::atomic<int> count{0};
+  std::atomic<int> sense{0};
+  void arrive_and_wait(int n, int& my_sense) {
+    my_sense ^= 1;
+    if (count.fetch_add(1, std::memory_order_acq_rel) == n - 1) {
+      count.store(0, std::memory_order_relaxed);
+      sense.store(my_sense, std::memory_order_release);
+    } else {
+      while (sense.load(std::memory_order_acquire) != my_sense) std::this_thread::yield();
+    }
+  }
+};
+}  // namespace
+
+extern "C" int hp_selftest_push(int world, int calls, int scheme) {
   if (world < 1 || world > TCCL_MAX_WORLD) return 100;
-  constexpr int kElems = 32;
+  constexpr int kCtas = 4;
+  constexpr int kSlotElems = 64;                 // capacity of one fixed slot
+  static const int kSizes[3] = {64, 32, 8};      // message elements of call n: kSizes[n % 3] ...
+  static const int kGrids[3] = {4, 2, 1};        // ... and its grid
+  const size_t region = (size_t)2 * world * kSlotElems;
   std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
   std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
-  std::vector<std::vector<float>> slots(world, std::vector<float>((size_t)2 * world * kElems, 0.f));
+  std::vector<std::vector<float>> slots(world, std::vector<float>(region, 0.f));
+  std::vector<KernelBoundary> boundary(world);
   std::atomic<int> bad{0};
   std::vector<std::thread> th;
+  auto val = [](int call, int r, int i) { return (float)(call * 100 + r * 10 + i % 3); };
   for (int r = 0; r < world; ++r)
-    th.emplace_back([&, r] {
-      HostComm c;
-      c.world = world;
-      c.rank = r;
-      for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
-      c.local = local[r].data();
-      c.timeout_ns = 20ull * 1000 * 1000 * 1000;
-      Faults none{-1, 0, -1};
-      for (int call = 0; call < calls; ++call) {
-        const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
-        const uint32_t e = c.local[TCCL_LOCAL_EPOCH + 0] + 1u;
-        const size_t base = (size_t)(e & 1u) * world * kElems;
-        for (int q = 0; q < world; ++q)
-          for (int i = 0; i < kElems; ++i) slots[q][base + (size_t)r * kElems + i] = (float)(call * 100 + r * 10 + i % 3);
-        if (!barrier(c, 0, deadline, none)) {
-          bad.store(1);
-          return;
-        }
-        for (int i = 0; i < kElems; ++i) {
-          float s = 0.f, want = 0.f;
-          for (int p = 0; p < world; ++p) {
-            s += slots[r][base + (size_t)p * kElems + i];
-            want += (float)(call * 100 + p * 10 + i % 3);
+    for (int bid = 0; bid < kCtas; ++bid)
+      th.emplace_back([&, r, bid] {
+        HostComm c;
+        c.world = world;
+        c.rank = r;
+        for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+        c.local = local[r].data();
+        c.timeout_ns = 20ull * 1000 * 1000 * 1000;
+        Faults none{-1, 0, -1};
+        int my_sense = 0;
+        for (int call = 0; call < calls; ++call) {
+          const int n = kSizes[call % 3], grid = kGrids[call % 3];
+          if (bid < grid && !bad.load(std::memory_order_relaxed)) {
+            const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+            size_t base, slot;
+            uint32_t seq = 0;
+            if (scheme == 0) {
+              seq = A(c.local + TCCL_LOCAL_PUSH_SEQ).load(std::memory_order_relaxed);
+              slot = kSlotElems;
+              base = (size_t)(seq & 1u) * (region / 2);
+            } else {
+              const uint32_t e = c.local[TCCL_LOCAL_EPOCH + bid] + 1u;
+              slot = (size_t)n;
+              base = (size_t)(e & 1u) * world * slot;
+            }
+            const int lo = n * bid / grid, hi = n * (bid + 1) / grid;  // this CTA's slab
+            for (int q = 0; q < world; ++q)
+              for (int i = lo; i < hi; ++i) slots[q][base + (size_t)r * slot + i] = val(call, r, i);
+            if (!barrier(c, bid, deadline, none)) {
+              bad.store(1);
+            } else {
+              for (int i = lo; i < hi; ++i) {
+                float s = 0.f, want = 0.f;
+                for (int p = 0; p < world; ++p) {
+                  s += slots[r][base + (size_t)p * slot + i];
+                  want += val(call, p, i);
+                }
+                if (s != want) bad.store(2);
+              }
+              if (scheme == 0) {
+                const uint32_t done = A(c.local + TCCL_LOCAL_PUSH_DONE).fetch_add(1u, std::memory_order_acq_rel);
+                if (done == (uint32_t)grid - 1u) {
+                  A(c.local + TCCL_LOCAL_PUSH_DONE).store(0u, std::memory_order_relaxed);
+                  A(c.local + TCCL_LOCAL_PUSH_SEQ).store(seq + 1u, std::memory_order_relaxed);
+                }
+              }
+            }
+            if ((call & 3) == (r + bid) % 4) std::this_thread::yield();  // let ranks and CTAs drift apart
           }
-          if (s != want) bad.store(2);
+          boundary[r].arrive_and_wait(kCtas, my_sense);  // the next kernel starts when this one is done
         }
-        if ((call & 3) == r % 4) std::this_thread::yield();  // let the ranks drift apart
-      }
-    });
+      });
   for (auto& x : th) x.join();
   return bad.load();
 }

@@ -2,13 +2,20 @@
 // meant to be built with -fsanitize=thread.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 
 extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds);
 extern "C" int hp_selftest_gemm_rs(int world, int ctas, int tiles_per_owner, int calls);
 extern "C" int hp_selftest_ag(int world, int movers, int consumers, int row_tiles, int calls);
-extern "C" int hp_selftest_push(int world, int calls);
+extern "C" int hp_selftest_push(int world, int calls, int scheme);
 
 int main(int argc, char** argv) {
+  if (argc > 2 && std::strcmp(argv[1], "push-broken-variant") == 0) {
+    // the size-dependent layout with a per-CTA epoch parity: expected to be reported as a race
+    const int rc = hp_selftest_push(std::atoi(argv[2]), 300, 1);
+    std::printf("hp_selftest_push(broken variant) -> %d\n", rc);
+    return rc;
+  }
   const int world = argc > 1 ? std::atoi(argv[1]) : 4;
   const int numel = argc > 2 ? std::atoi(argv[2]) : 1 << 14;
   const int chunk = argc > 3 ? std::atoi(argv[3]) : 1 << 9;
@@ -21,7 +28,7 @@ int main(int argc, char** argv) {
   rc = hp_selftest_ag(world, 3, 4, 4, 3);
   std::printf("hp_selftest_ag(world=%d) -> %d\n", world, rc);
   if (rc) return rc;
-  rc = hp_selftest_push(world, 200);
+  rc = hp_selftest_push(world, 300, 0);
   std::printf("hp_selftest_push(world=%d) -> %d\n", world, rc);
   return rc;
 }

@@ -37,7 +37,8 @@ extern "C" {
 #define TCCL_FLAG_LL (TCCL_FLAG_TILE + TCCL_MAX_WORLD * TCCL_MAX_TILES) /* misc / p2p */
 #define TCCL_FLAG_AG (TCCL_FLAG_LL + 1024)                            /* [src][row tile] AG->GEMM */
 #define TCCL_MAX_ROW_TILES 256
-#define TCCL_FLAG_WORDS (TCCL_FLAG_AG + TCCL_MAX_WORLD * TCCL_MAX_ROW_TILES)
+#define TCCL_FLAG_TREE_ACK (TCCL_FLAG_AG + TCCL_MAX_WORLD * TCCL_MAX_ROW_TILES) /* [tree][cta]: my chunks the parent has consumed */
+#define TCCL_FLAG_WORDS (TCCL_FLAG_TREE_ACK + 2 * TCCL_TREE_MAX_CTAS)
 
 /* local (non peer-visible) state, in 32-bit words */
 #define TCCL_LOCAL_EPOCH 0                                       /* [block] p2p barrier   */
@@ -46,7 +47,10 @@ extern "C" {
 #define TCCL_LOCAL_TILE_EPOCH (TCCL_LOCAL_STATUS + 16)           /* 1 word: tile epoch    */
 #define TCCL_LOCAL_SCHED (TCCL_LOCAL_TILE_EPOCH + 1)             /* [0] CTAs of a fused kernel that are done */
 #define TCCL_LOCAL_AGCNT (TCCL_LOCAL_SCHED + 63)                 /* [row tile] data movers done (AG->GEMM) */
-#define TCCL_LOCAL_WORDS (TCCL_LOCAL_AGCNT + TCCL_MAX_ROW_TILES)
+#define TCCL_LOCAL_PUSH_SEQ (TCCL_LOCAL_AGCNT + TCCL_MAX_ROW_TILES) /* push all-reduce calls completed (slot parity) */
+#define TCCL_LOCAL_PUSH_DONE (TCCL_LOCAL_PUSH_SEQ + 1)           /* CTAs of the running push all-reduce that are done */
+#define TCCL_LOCAL_TREE_SEQ (TCCL_LOCAL_PUSH_DONE + 1)           /* [role][cta]: chunks this pipeline moved in earlier calls */
+#define TCCL_LOCAL_WORDS (TCCL_LOCAL_TREE_SEQ + 4 * TCCL_TREE_MAX_CTAS)
 
 enum tccl_status_word {
   TCCL_ST_CODE = 0,   /* 0 = ok, else tccl_error */
@@ -80,9 +84,15 @@ typedef struct tccl_comm {
   uint32_t* local;                 /* this rank's private state (TCCL_LOCAL_*) */
   char* stage[TCCL_MAX_WORLD];     /* every rank's staging area, peer-mapped */
   char* mc_stage;                  /* multicast alias of the staging area, or NULL */
-  uint64_t stage_bytes;
+  uint64_t stage_bytes;            /* bytes of the staging area the fused kernels may use */
   uint64_t timeout_ns;
+  uint64_t ll_bytes;               /* bytes of the small-message region that follows: stage[p] + stage_bytes */
+  uint64_t tree_bytes;             /* bytes of the double-tree ring that follows the small-message region */
 } tccl_comm;
+
+/* double-tree ring: slot [tree][child slot][cta][chunk % depth], each TCCL_TREE_SLICE_BYTES long */
+#define TCCL_TREE_SLICE_BYTES 65536
+#define TCCL_TREE_RING_DEPTH 4
 
 /* Arguments shared by the data collectives. */
 typedef struct tccl_coll_args {
@@ -111,6 +121,8 @@ typedef struct tccl_launch {
 int tccl_version(void);
 const char* tccl_error_string(int code);
 int tccl_num_sms(void);
+/* sizeof of an ABI struct by its name ("tccl_comm", ...), -1 if unknown */
+int tccl_sizeof(const char* name);
 
 /* ---- barriers -------------------------------------------------------- */
 typedef struct tccl_barrier_args {
@@ -133,8 +145,11 @@ int tccl_wait_never(const tccl_comm*, const tccl_barrier_args*, const tccl_launc
 int tccl_allreduce_oneshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_oneshot_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 /* small-message latency path: push into the peers' staging slots, one barrier, local sum.
- * out_peer[p] / mc_out = rank p's slot region (2 parities x world x message bytes) / its multicast
- * alias; in[rank] = the local input (any device memory); numel * sizeof(T) % 16 == 0 */
+ * The slots live in the small-message region of the communicator (comm->stage[p] + comm->stage_bytes,
+ * comm->ll_bytes long): two halves used alternately from call to call, each cut into `world` slots of
+ * tccl_push_slot_bytes() whatever the message size.  in[rank] = the local input (any device
+ * memory); numel * sizeof(T) % 16 == 0 and at most one slot. */
+uint64_t tccl_push_slot_bytes(uint64_t ll_bytes, int world);
 int tccl_allreduce_push_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_twoshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
@@ -147,18 +162,21 @@ int tccl_reducescatter_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_
 
 /* ---- double-binary-tree all-reduce --------------------------------------- */
 typedef struct tccl_tree_args {
-  void* buf[TCCL_MAX_WORLD]; /* every rank's symmetric buffer; reduced in place */
-  void* out;                 /* optional local copy of the result, or NULL */
+  const void* in;            /* this rank's input: any device memory; may be buf[rank] (in place) */
+  void* buf[TCCL_MAX_WORLD]; /* every rank's result buffer (symmetric): parents store the sum into their children's */
+  void* out;                 /* optional local copy of the result in ordinary memory, or NULL */
   uint64_t numel;            /* a whole number of 16-byte vectors */
-  uint64_t chunk_vecs;       /* 16-byte vectors per chunk; chunk c uses tree c % 2 */
+  uint64_t chunk_vecs;       /* 16-byte vectors per chunk (<= ctas_per_role * TCCL_TREE_SLICE_BYTES / 16); chunk c uses tree c % 2 */
   int32_t dtype;
-  int32_t ctas_per_role;     /* K; the grid is 4 K CTAs (up/down x tree 0/1), K <= TCCL_TREE_MAX_CTAS */
+  int32_t ctas_per_role;     /* K; the grid is 4 K CTAs (up/down x tree 0/1); K <= tccl_tree_max_ctas(comm->tree_bytes) */
   int32_t parent[2];         /* neighbours in tree 0 / 1, -1 = none */
   int32_t left[2];
   int32_t right[2];
   int32_t child_slot[2];     /* 0 if this rank is its parent's left child, 1 if right */
 } tccl_tree_args;
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
+/* CTAs per role that a ring of `tree_bytes` can serve (<= TCCL_TREE_MAX_CTAS) */
+int tccl_tree_max_ctas(uint64_t tree_bytes);
 
 /* ---- fused all-reduce + bias + residual + RMSNorm ------------------------- */
 typedef struct tccl_arn_args {

@@ -21,7 +21,7 @@ from typing import Callable, Optional
 
 import torch
 
-from ..parallel.world import WorldBase
+from ..parallel.world import PlanCache, WorldBase  # noqa: F401  (PlanCache re-exported for tests)
 from ..utils import lib as L
 from ._common import check_sym_tensor, debug_log, dtype_code, get_world, grid_for
 
@@ -41,8 +41,16 @@ _AR_KERNELS = {
 }
 
 
+_X, _OUT = "<the caller's input>", "<the caller's out>"  # Plan.result: hand back an argument of the call
+
+
 class Plan:
-    """A bound launch.  ``run(out)``: ``out`` None → use/allocate the planned output."""
+    """A bound launch.  ``run(x, out)`` enqueues it; ``x`` / ``out`` are the tensors of THIS call.
+
+    A plan holds raw addresses, not the caller's ordinary tensors: an activation that was
+    all-reduced once must stay free-able, or the caching allocator could never reuse its
+    address and every call would plan (and pin) another one.  Tensors in symmetric memory
+    may be referenced: the communicator keeps those allocations alive anyway."""
 
     __slots__ = ("go", "args", "world", "result", "alloc", "post", "custom")
 
@@ -50,9 +58,9 @@ class Plan:
         self.world, self.go, self.args, self.result, self.alloc, self.post = world, go, args, result, alloc, post
         self.custom = custom  # a complete replacement of run(), for plans that do not fit the pattern
 
-    def run(self):
+    def run(self, x=None, out=None):
         if self.custom is not None:
-            return self.custom()
+            return self.custom(x, out)
         if self.alloc is not None:  # fresh local output(s) per call
             outs = {}
             for r, a in self.args.items():
@@ -63,24 +71,32 @@ class Plan:
             return self.world.wrap(outs)
         self.go()
         if self.post is not None:
-            self.post()
-        return self.result
+            self.post(x, out)
+        res = self.result
+        return x if res is _X else (out if res is _OUT else res)
+
+
+def _tkey(t):
+    """Address, extent AND layout: a strided view that shares address, element count and dtype
+    with a contiguous tensor must not hit that tensor's plan."""
+    return (t.data_ptr(), tuple(t.shape), tuple(t.stride()), t.dtype)
 
 
 def _key(tag, w, x, out, *rest):
     x0 = w.local(x, w.local_ranks[0])
     o0 = None if out is None else w.local(out, w.local_ranks[0])
-    return (tag, x0.data_ptr(), x0.numel(), x0.dtype, 0 if o0 is None else o0.data_ptr(), *rest)
+    return (tag, _tkey(x0), None if o0 is None else _tkey(o0), *rest)
 
 
-def _cached(w: WorldBase, key, build: Callable[[], Plan]):
+def _cached(w: WorldBase, key, build: Callable[[], Plan], x=None, out=None):
     plans = w.plans
     if plans is None:
-        return build().run()
-    p = plans.get(key)
+        return build().run(x, out)
+    p = plans.lookup(key)
     if p is None:
-        p = plans[key] = build()
-    return p.run()
+        p = build()
+        plans.insert(key, p)
+    return p.run(x, out)
 
 
 def _base_args(world: WorldBase, x, dt: int, flags: int) -> L.CollArgs:
@@ -129,7 +145,7 @@ def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -
     nvls = world.has_nvls
     if world.world_size == 1:
         return "oneshot_p2p"
-    if nbytes <= cfg.push_max_bytes and nbytes % 16 == 0 and 2 * world.world_size * nbytes <= world.ll_bytes:
+    if nbytes <= cfg.push_max_bytes and nbytes % 16 == 0 and nbytes <= world.push_max_bytes():
         return "push_nvls" if nvls and world.world_size > 2 else "push_p2p"
     if not symmetric_dst or nbytes <= cfg.oneshot_max_bytes:
         return "oneshot_nvls" if nvls and world.world_size > 2 and nbytes <= 4 * cfg.oneshot_max_bytes else "oneshot_p2p"
@@ -155,7 +171,7 @@ def all_reduce(x, out=None, *, inplace: bool = False, algo: str = "auto", world:
 
         return double_tree_all_reduce(x, out=out, inplace=inplace, world=w)
     return _cached(w, _key("ar", w, x, out, inplace, algo, sync_exit),
-                   lambda: _plan_all_reduce(w, x, out, inplace, algo, sync_exit))
+                   lambda: _plan_all_reduce(w, x, out, inplace, algo, sync_exit), x, out)
 
 
 def _plan_push(w, x, out, inplace, algo) -> Plan:
@@ -167,18 +183,14 @@ def _plan_push(w, x, out, inplace, algo) -> Plan:
     W = w.world_size
     if not x0.is_contiguous() or x0.data_ptr() % 16 or nbytes % 16:
         raise ValueError("push all-reduce needs a contiguous, 16-byte aligned input of a multiple of 16 bytes")
-    if 2 * W * nbytes > w.ll_bytes:
-        raise ValueError(f"push all-reduce handles at most {w.ll_bytes // (2 * W)} bytes per rank")
+    if nbytes > w.push_max_bytes():
+        raise ValueError(f"push all-reduce handles at most {w.push_max_bytes()} bytes per rank")
     if algo == "push_nvls" and not w.has_nvls:
         raise RuntimeError("push_nvls needs NVLS multicast")
-    slots, mc = w.ll_ptrs(), w.ll_mc()
     args = {}
     for r in w.local_ranks:
         a = L.CollArgs()
-        a.inp[r] = locs[r].data_ptr()
-        for p, v in enumerate(slots):
-            a.out_peer[p] = v
-        a.mc_out = mc
+        a.inp[r] = locs[r].data_ptr()  # the slots are found through the communicator itself
         a.numel, a.dtype, a.flags = x0.numel(), dt, w.coll_flags()
         args[r] = a
     nvec = nbytes // 16
@@ -189,14 +201,15 @@ def _plan_push(w, x, out, inplace, algo) -> Plan:
     if inplace:
         for r, a in args.items():
             a.out = locs[r].data_ptr()  # each vector is read (into the slots) before the barrier, written after
-        return Plan(w, go, args, result=x)
+        return Plan(w, go, args, result=_X)
     if out is not None:
         for r, a in args.items():
             o = w.local(out, r)
             _check_out(o, locs[r])
             a.out = o.data_ptr()
-        return Plan(w, go, args, result=out)
-    return Plan(w, go, args, alloc=lambda r: torch.empty_like(locs[r]))
+        return Plan(w, go, args, result=_OUT)
+    shape, dtype, dev = tuple(x0.shape), x0.dtype, x0.device  # no reference to the caller's tensor
+    return Plan(w, go, args, alloc=lambda r: torch.empty(shape, dtype=dtype, device=dev))
 
 
 def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
@@ -241,18 +254,19 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
             for r, a in args.items():
                 a.out = tmp[r].data_ptr()
 
-            def post():
+            def post(x_, _out):
                 for r in w.local_ranks:
-                    w.local(x, r).copy_(tmp[r])
+                    w.local(x_, r).copy_(tmp[r])
 
-            return Plan(w, go, args, result=x, post=post)
+            return Plan(w, go, args, result=_X, post=post)
         if out is not None:
             for r, a in args.items():
                 o = w.local(out, r)
                 _check_out(o, w.local(x, r))
                 a.out = o.data_ptr()
-            return Plan(w, go, args, result=out)
-        return Plan(w, go, args, alloc=lambda r: torch.empty_like(w.local(x, r)))
+            return Plan(w, go, args, result=_OUT)
+        shape, dtype, dev = tuple(x0.shape), x0.dtype, x0.device
+        return Plan(w, go, args, alloc=lambda r: torch.empty(shape, dtype=dtype, device=dev))
     # two-shot: destination must be symmetric
     if not sym_dst:
         raise ValueError("two-shot all-reduce writes into symmetric memory: pass inplace=True or a symmetric out")
@@ -275,7 +289,7 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
     else:
         grid = grid_for(w, per_slice, block, 2 if w.world_size >= 8 else 4)
     debug_log(w, f"all_reduce {nbytes} B -> {algo}, grid {grid} x {block}")
-    return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt), args, result=dst)
+    return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt), args, result=_X if inplace else _OUT)
 
 
 def _plan_staged_twoshot(w, x, out, sync_exit) -> Plan:
@@ -293,15 +307,17 @@ def _plan_staged_twoshot(w, x, out, sync_exit) -> Plan:
         for r in w.local_ranks:
             _check_out(w.local(out, r), w.local(x, r))
 
-        def post():
+        def post(_x, out_):
             for r in w.local_ranks:
-                w.local(out, r).view(-1).copy_(w.local(buf, r))
+                w.local(out_, r).view(-1).copy_(w.local(buf, r))
 
-        return Plan(w, inner.go, inner.args, result=out, post=post)
+        return Plan(w, inner.go, inner.args, result=_OUT, post=post)
 
-    def run_fresh():  # a new output tensor per call, filled from the symmetric buffer
+    shape, dtype, dev = tuple(x0.shape), x0.dtype, x0.device
+
+    def run_fresh(_x, _out):  # a new output tensor per call, filled from the symmetric buffer
         inner.go()
-        outs = {r: torch.empty_like(w.local(x, r)) for r in w.local_ranks}
+        outs = {r: torch.empty(shape, dtype=dtype, device=dev) for r in w.local_ranks}
         for r, o in outs.items():
             o.view(-1).copy_(w.local(buf, r))
         return w.wrap(outs)
@@ -319,7 +335,7 @@ def all_gather(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = 
     trips), pull otherwise.
     """
     w = get_world(world)
-    return _cached(w, _key("ag", w, x, out, algo, sync_exit), lambda: _plan_all_gather(w, x, out, algo, sync_exit))
+    return _cached(w, _key("ag", w, x, out, algo, sync_exit), lambda: _plan_all_gather(w, x, out, algo, sync_exit), x, out)
 
 
 def _plan_all_gather(w, x, out, algo, sync_exit) -> Plan:
@@ -347,7 +363,7 @@ def _plan_all_gather(w, x, out, algo, sync_exit) -> Plan:
                 o = w.local(out, r)
                 _check_out(o, w.local(x, r), x0.numel() * W)
                 a.out = o.data_ptr()
-            return Plan(w, go, args, result=out)
+            return Plan(w, go, args, result=_OUT)
         shape = (W, *x0.shape)
         return Plan(w, go, args, alloc=lambda r: torch.empty(shape, dtype=x0.dtype, device=x0.device))
     if algo not in ("push", "push_nvls"):
@@ -370,7 +386,7 @@ def _plan_all_gather(w, x, out, algo, sync_exit) -> Plan:
         a.mc_out = w.mc_ptr(out)
         args[r] = a
     name = "tccl_allgather_push_nvls" if algo == "push_nvls" else "tccl_allgather_push_p2p"
-    return Plan(w, w.prepare(name, args, grid_for(w, nvec, block, 4), block, dt), args, result=out)
+    return Plan(w, w.prepare(name, args, grid_for(w, nvec, block, 4), block, dt), args, result=_OUT)
 
 
 def reduce_scatter(x, out=None, *, algo: str = "auto", world: Optional[WorldBase] = None, sync_exit: bool = True):
@@ -379,7 +395,8 @@ def reduce_scatter(x, out=None, *, algo: str = "auto", world: Optional[WorldBase
     As in the reference the element count must be a multiple of ``W`` times the
     16-byte vector width (``triton_reduce_scatter.py:102-104``)."""
     w = get_world(world)
-    return _cached(w, _key("rs", w, x, out, algo, sync_exit), lambda: _plan_reduce_scatter(w, x, out, algo, sync_exit))
+    return _cached(w, _key("rs", w, x, out, algo, sync_exit), lambda: _plan_reduce_scatter(w, x, out, algo, sync_exit),
+                   x, out)
 
 
 def _plan_reduce_scatter(w, x, out, algo, sync_exit) -> Plan:
@@ -408,7 +425,7 @@ def _plan_reduce_scatter(w, x, out, algo, sync_exit) -> Plan:
             o = w.local(out, r)
             _check_out(o, w.local(x, r), per)
             a.out = o.data_ptr()
-        return Plan(w, go, args, result=out)
+        return Plan(w, go, args, result=_OUT)
     return Plan(w, go, args, alloc=lambda r: torch.empty(per, dtype=x0.dtype, device=x0.device))
 
 

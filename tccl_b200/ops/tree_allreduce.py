@@ -7,68 +7,82 @@ reference only sketches: the neighbours come from
 reference hard-codes 8 and a global ``rank``), and the kernel really reduces up
 and broadcasts down both trees.
 
-The reduction happens in place in the symmetric buffer (partials overwrite the
-rank's own data on the way up), so by default the input is first copied into a
-scratch symmetric buffer and the result is returned as a new tensor, leaving
-``tensor`` intact like the reference's wrapper; ``inplace=True`` reduces
-``tensor`` itself and skips the copy.
+Data moves by stores into the receiver's memory only: a rank reads nothing but
+its own input, partial sums travel through a ring in the communicator's
+workspace, and a parent stores the final value into its children's *result
+buffer*, which therefore lives in symmetric memory: ``tensor`` itself with
+``inplace=True``, else a scratch buffer shared by all calls of one size, from
+which the kernel copies each slice into an ordinary output tensor (a fresh one
+per call unless ``out=`` is given), so ``tensor`` stays intact like the
+reference's wrapper and two results never alias.  Only the in-place form needs
+``tensor`` in symmetric memory.
 """
 from __future__ import annotations
 
 from typing import Optional
 
+import torch
+
 from ..parallel.tree import tree_neighbours
 from ..parallel.world import WorldBase
 from ..utils import lib as L
 from ._common import K, check_sym_tensor, dtype_code, get_world
-from .collectives import Plan, _cached, _check_out, _key
+from .collectives import _OUT, _X, Plan, _cached, _check_out, _key
 
 __all__ = ["double_tree_all_reduce"]
 
+_SLICE = K["TCCL_TREE_SLICE_BYTES"]
+
 
 def _tree_grid(w: WorldBase, nbytes: int):
-    """(K, chunk_vecs): CTAs per role and 16-byte vectors per chunk."""
+    """(K, chunk_vecs): CTAs per role and 16-byte vectors per chunk.  A CTA moves at most one
+    ring slice (64 KiB) of a chunk; small messages use few CTAs (latency), large ones all the
+    ring serves, with at least four chunks per tree so that the up and down phases overlap."""
     cfg = w.config
-    kmax = min(cfg.tree_ctas, K["TCCL_TREE_MAX_CTAS"], max(1, w.max_ctas() // 4))
-    # at least 64 KiB per CTA per chunk, or the per-chunk handshake dominates
-    k = max(1, min(kmax, nbytes // (2 * 65536)))
-    if cfg.tree_chunk_bytes < 65536:
-        chunk_bytes = cfg.tree_chunk_bytes  # small chunks on request (tests of the pipeline)
-    else:
-        floor = k * 65536
-        # keep several chunks per tree in flight even for medium messages
-        chunk_bytes = max(floor, min(cfg.tree_chunk_bytes, nbytes // 8))
-    chunk_vecs = max(1, chunk_bytes // 16)
-    return k, chunk_vecs
+    kmax = max(1, min(cfg.tree_ctas, K["TCCL_TREE_MAX_CTAS"], max(1, w.max_ctas() // 4)))
+    per_tree = max(16, nbytes // 2)
+    if cfg.tree_chunk_bytes < _SLICE:  # small chunks on request (tests of the pipeline)
+        chunk_bytes = max(16, cfg.tree_chunk_bytes // 16 * 16)
+        k = max(1, min(kmax, chunk_bytes // 16))
+        return k, chunk_bytes // 16
+    k = max(1, min(kmax, per_tree // 32768))
+    slice_bytes = max(4096, min(_SLICE, per_tree // k // 4, cfg.tree_chunk_bytes // k))
+    slice_bytes = max(16, slice_bytes // 16 * 16)
+    return k, k * slice_bytes // 16
 
 
 def double_tree_all_reduce(tensor, out=None, *, inplace: bool = False, world: Optional[WorldBase] = None):
     w = get_world(world)
-    return _cached(w, _key("tree", w, tensor, out, inplace), lambda: _plan(w, tensor, out, inplace))
+    return _cached(w, _key("tree", w, tensor, out, inplace), lambda: _plan(w, tensor, out, inplace), tensor, out)
 
 
 def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
-    check_sym_tensor(w, x, "double_tree_all_reduce input")
+    if inplace:
+        check_sym_tensor(w, x, "double_tree_all_reduce input")
     x0 = w.local(x, w.local_ranks[0])
+    if not x0.is_cuda or not x0.is_contiguous() or x0.data_ptr() % 16:
+        raise ValueError("the input must be a contiguous, 16-byte aligned CUDA tensor")
     dt = dtype_code(x0.dtype)
     nbytes = x0.numel() * x0.element_size()
     if nbytes % 16:
         raise ValueError("the element count must be a whole number of 16-byte vectors")
     W = w.world_size
-    work = x
-    pre = None
-    if not inplace:
-        # reduce inside a scratch symmetric buffer so that the caller's tensor survives
-        work = w.empty(x0.shape, x0.dtype)
-
-        def pre():
-            for r in w.local_ranks:
-                w.local(work, r).copy_(w.local(x, r))
+    if inplace:
+        work = x
+    else:
+        # the result buffer that parents store into: one scratch per size and dtype; every
+        # call copies its result out inside the kernel, so sharing it is safe
+        cache = w.__dict__.setdefault("_tree_work", {})
+        key = (x0.numel(), x0.dtype)
+        work = cache.get(key)
+        if work is None:
+            work = cache[key] = w.empty(x0.numel(), x0.dtype)
     ptrs = w.peer_ptrs(work)
     k, chunk_vecs = _tree_grid(w, nbytes)
     args = {}
     for r in w.local_ranks:
         a = L.TreeArgs()
+        a.inp = w.local(x, r).data_ptr()
         for p, v in enumerate(ptrs):
             a.buf[p] = v
         a.numel = x0.numel()
@@ -87,12 +101,9 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
             a.out = o.data_ptr()
         args[r] = a
     go = w.prepare("tccl_allreduce_tree", args, 4 * k, w.config.block, dt)
-    result = out if out is not None else work
-    if pre is None:
-        return Plan(w, go, args, result=result)
-
-    def go2():
-        pre()
-        go()
-
-    return Plan(w, go2, args, result=result)
+    if out is not None:
+        return Plan(w, go, args, result=_OUT)
+    if inplace:
+        return Plan(w, go, args, result=_X)
+    shape, dtype, dev = tuple(x0.shape), x0.dtype, x0.device
+    return Plan(w, go, args, alloc=lambda r: torch.empty(shape, dtype=dtype, device=dev))

@@ -18,7 +18,7 @@ import torch
 
 from ..config import Config
 from ..utils import lib as L
-from .world import WorldBase, _status_dict
+from .world import WorldBase, _status_dict, tree_ring_bytes
 
 K = L.K
 
@@ -69,7 +69,10 @@ class EmuWorld(WorldBase):
         self._flag_words = K["TCCL_FLAG_WORDS"]
         self._stage_bytes = int(self.config.stage_mb) << 20
         self.flags = [torch.zeros(self._flag_words, dtype=torch.int32, device=self.device) for _ in range(W)]
-        self.stages = [torch.empty(self._stage_bytes, dtype=torch.uint8, device=self.device) for _ in range(W)]
+        self.tree_bytes = tree_ring_bytes(self.config)
+        # one allocation per rank: [staging area (its tail is the small-message region) | double-tree ring]
+        self.stages = [torch.empty(self._stage_bytes + self.tree_bytes, dtype=torch.uint8, device=self.device)
+                       for _ in range(W)]
         self.local_states = [torch.zeros(K["TCCL_LOCAL_WORDS"], dtype=torch.int32, device=self.device) for _ in range(W)]
         self.ll_bytes = min(2 << 20, self._stage_bytes // 4)
         self._keep = []
@@ -90,6 +93,8 @@ class EmuWorld(WorldBase):
             c.local = self.local_states[r].data_ptr()
             c.stage_bytes = self._stage_bytes - self.ll_bytes
             c.timeout_ns = self.config.timeout_ns
+            c.ll_bytes = self.ll_bytes
+            c.tree_bytes = self.tree_bytes
         self._comms_host = arr
         self.comms_dev = self._to_device(arr)
 

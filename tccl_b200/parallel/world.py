@@ -23,6 +23,7 @@ is resolved once and cached.
 from __future__ import annotations
 
 import ctypes as C
+from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -44,6 +45,31 @@ def _status_dict(words: Sequence[int]) -> dict:
         "want": int(words[K["TCCL_ST_WANT"]]),
         "aborted": bool(words[K["TCCL_ST_ABORT"]]),
     }
+
+
+class PlanCache(OrderedDict):
+    """Least-recently-used cache of plans (``Config.plan_cache_size`` entries)."""
+
+    def __init__(self, maxsize: int = 512):
+        super().__init__()
+        self.maxsize = max(1, int(maxsize))
+
+    def lookup(self, key):
+        p = self.get(key)
+        if p is not None:
+            self.move_to_end(key)
+        return p
+
+    def insert(self, key, plan):
+        self[key] = plan
+        while len(self) > self.maxsize:
+            self.popitem(last=False)
+
+
+def tree_ring_bytes(config: Config) -> int:
+    """Bytes of the double-tree ring: [tree][child slot][cta][depth] slices for ``tree_ctas`` CTAs per role."""
+    k = max(1, min(int(config.tree_ctas), K["TCCL_TREE_MAX_CTAS"]))
+    return 4 * k * K["TCCL_TREE_RING_DEPTH"] * K["TCCL_TREE_SLICE_BYTES"]
 
 
 class WorldBase:
@@ -104,6 +130,11 @@ class WorldBase:
         """A one-rank collective is a local copy: HBM-bound, wants several CTAs per SM."""
         return min(4 * self.max_ctas(), K["TCCL_MAX_BLOCKS"])
 
+    def push_max_bytes(self) -> int:
+        """Largest message of the push all-reduce: one slot of the small-message region
+        (two alternating halves of ``world_size`` fixed slots each)."""
+        return (self.ll_bytes // 2 // self.world_size) & ~15
+
     def coll_flags(self, sync_entry: bool = True, sync_exit: bool = True) -> int:
         f = 0
         if not sync_entry:
@@ -135,16 +166,22 @@ class RealWorld(WorldBase):
             raise ValueError(f"world size {self.world_size} > {L.MAX_WORLD}")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         L.lib()  # fail loudly if the native library is absent
-        try:  # still needed by older symmetric-memory builds; a no-op on newer ones
-            symm_mem.enable_symm_mem_for_group(self.group.group_name)
-        except Exception:
+        try:  # still needed by older symmetric-memory builds; newer ones only warn that it is deprecated
+            import warnings
+
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                symm_mem.enable_symm_mem_for_group(self.group.group_name)
+        except (AttributeError, TypeError):  # the function is gone or changed its signature: nothing to enable
             pass
         self._handles: Dict[int, tuple] = {}
-        self.plans: Dict[tuple, object] = {}  # op wrappers cache their bound launches here
+        self.plans = PlanCache(self.config.plan_cache_size)  # op wrappers cache their bound launches here
         # workspace = [flag region | staging area], one symmetric allocation
         self._flag_bytes = -(-K["TCCL_FLAG_WORDS"] * 4 // 65536) * 65536
         self._stage_bytes = int(self.config.stage_mb) << 20
-        self.workspace = symm_mem.empty(self._flag_bytes + self._stage_bytes, dtype=torch.uint8, device=self.device)
+        self.tree_bytes = tree_ring_bytes(self.config)
+        self.workspace = symm_mem.empty(self._flag_bytes + self._stage_bytes + self.tree_bytes, dtype=torch.uint8,
+                                        device=self.device)
         self.workspace[: self._flag_bytes].zero_()
         self.local_state = torch.zeros(K["TCCL_LOCAL_WORDS"], dtype=torch.int32, device=self.device)
         ptrs, mc = self._resolve(self.workspace)
@@ -162,6 +199,8 @@ class RealWorld(WorldBase):
         self.ll_bytes = min(2 << 20, self._stage_bytes // 4)
         comm.stage_bytes = self._stage_bytes - self.ll_bytes
         comm.timeout_ns = self.config.timeout_ns
+        comm.ll_bytes = self.ll_bytes
+        comm.tree_bytes = self.tree_bytes  # the double-tree ring follows the staging area
         self.comm = comm
         self._stage_ptrs = [ptrs[p] + self._flag_bytes for p in range(self.world_size)]
         self._stage_mc = (mc + self._flag_bytes) if mc else 0

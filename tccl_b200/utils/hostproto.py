@@ -24,7 +24,8 @@ class HpFaults(C.Structure):
 
 
 class HpTree(C.Structure):
-    _fields_ = [("buf", C.c_uint64 * MAXW), ("numel", C.c_uint64), ("chunk", C.c_uint64),
+    _fields_ = [("inp", C.c_uint64), ("buf", C.c_uint64 * MAXW), ("ring", C.c_uint64 * MAXW),
+                ("numel", C.c_uint64), ("chunk", C.c_uint64), ("ring_stride", C.c_uint64),
                 ("parent", C.c_int32 * 2), ("left", C.c_int32 * 2), ("right", C.c_int32 * 2),
                 ("child_slot", C.c_int32 * 2)]
 
@@ -41,12 +42,15 @@ def _lib(path: Optional[str] = None) -> C.CDLL:
 
 
 def layout(world: int, numel: int):
-    """Byte offsets inside the shared block: flag regions, private words, data buffers."""
+    """Byte offsets inside the shared block: flag regions, private words, data buffers, and the
+    double-tree rings (sized for chunks of up to ``numel`` elements)."""
     fb, lb, db = K["TCCL_FLAG_WORDS"] * 4, K["TCCL_LOCAL_WORDS"] * 4, numel * 4
+    rb = 4 * K["TCCL_TREE_RING_DEPTH"] * db
     flags = [r * fb for r in range(world)]
     local = [world * fb + r * lb for r in range(world)]
     data = [world * (fb + lb) + r * db for r in range(world)]
-    return flags, local, data, world * (fb + lb + db)
+    rings = [world * (fb + lb + db) + r * rb for r in range(world)]
+    return flags, local, data, rings, world * (fb + lb + db + rb)
 
 
 def _status(buf, off) -> dict:
@@ -63,7 +67,7 @@ def _rank_main(lib_path: str, shm_name: str, world: int, rank: int, numel: int, 
     shm = shared_memory.SharedMemory(name=shm_name)
     try:
         base = C.addressof(C.c_char.from_buffer(shm.buf))
-        flags, local, data, _ = layout(world, numel)
+        flags, local, data, rings, _ = layout(world, numel)
         lib = _lib(lib_path)
         comm = HpComm()
         comm.world, comm.rank = world, rank
@@ -79,9 +83,12 @@ def _rank_main(lib_path: str, shm_name: str, world: int, rank: int, numel: int, 
             ok = lib.hp_barrier(C.byref(comm), 0, int(faults.get("rounds", 1)), C.byref(f))
         else:
             t = HpTree()
+            t.inp = base + data[rank]  # in place: the result buffer is the input
             for p in range(world):
                 t.buf[p] = base + data[p]
+                t.ring[p] = base + rings[p]
             t.numel, t.chunk = numel, int(faults.get("chunk", max(1, numel // 16)))
+            t.ring_stride = numel
             for tr in (0, 1):
                 parent, left, right = tree_neighbours(world, rank, tr)
                 t.parent[tr], t.left[tr], t.right[tr] = parent, left, right
@@ -101,7 +108,7 @@ def run_ranks(world: int, op: str, numel: int = 0, inputs: Optional[List[np.ndar
 
     lib_path = str(B.build_host())  # built once here; the ranks only load it
     faults = faults or {}
-    flags, local, data, total = layout(world, numel)
+    flags, local, data, rings, total = layout(world, numel)
     shm = shared_memory.SharedMemory(create=True, size=max(total, 4096))
     try:
         np.frombuffer(shm.buf, dtype=np.uint8)[:] = 0

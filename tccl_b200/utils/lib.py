@@ -30,6 +30,8 @@ class Comm(C.Structure):
         ("mc_stage", C.c_uint64),
         ("stage_bytes", C.c_uint64),
         ("timeout_ns", C.c_uint64),
+        ("ll_bytes", C.c_uint64),
+        ("tree_bytes", C.c_uint64),
     ]
 
 
@@ -56,6 +58,7 @@ class PadsArgs(C.Structure):
 
 class TreeArgs(C.Structure):
     _fields_ = [
+        ("inp", C.c_uint64),
         ("buf", C.c_uint64 * MAX_WORLD),
         ("out", C.c_uint64),
         ("numel", C.c_uint64),
@@ -156,8 +159,3 @@ def check(code: int, what: str) -> None:
     if code != 0:
         msg = lib().tccl_error_string(code).decode()
         raise TcclError(f"{what}: {msg} (code {code})")
-
-
-def call(name: str, comm_ptr, args_ptr, launch: Launch) -> None:
-    fn = getattr(lib(), name)
-    check(fn(comm_ptr, args_ptr, C.byref(launch)), name)

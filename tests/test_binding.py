@@ -14,10 +14,16 @@ def test_header_constants():
 
 
 def test_struct_layout_matches_c():
-    # 2 x int32 + 8 ptr + ptr + ptr + 8 ptr + ptr + 2 x u64
-    assert C.sizeof(L.Comm) == 8 + 8 * 8 + 8 + 8 + 8 * 8 + 8 + 16
-    assert C.sizeof(L.CollArgs) == 8 * 8 + 8 + 8 + 8 * 8 + 8 + 8 + 8
-    assert C.sizeof(L.Launch) == 24
+    """Every ctypes mirror has the size the compiler gives the C struct."""
+    lib = L.lib()
+    lib.tccl_sizeof.argtypes = [C.c_char_p]
+    pairs = {"tccl_comm": L.Comm, "tccl_coll_args": L.CollArgs, "tccl_launch": L.Launch,
+             "tccl_barrier_args": L.BarrierArgs, "tccl_pads_args": L.PadsArgs, "tccl_tree_args": L.TreeArgs,
+             "tccl_arn_args": L.ArnArgs, "tccl_gemm_args": L.GemmArgs, "tccl_gemm_rs_args": L.GemmRsArgs,
+             "tccl_ag_gemm_args": L.AgGemmArgs}
+    for name, mirror in pairs.items():
+        assert lib.tccl_sizeof(name.encode()) == C.sizeof(mirror), name
+    assert lib.tccl_sizeof(b"no_such_struct") == -1
 
 
 def test_config_env(monkeypatch):

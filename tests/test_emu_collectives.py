@@ -274,7 +274,12 @@ def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb):
             assert bool((err <= ref.abs() * TOL[dtype] * steps + (2e-2 if dtype != torch.float32 else 1e-5) * steps).all())
             assert torch.equal(out[r], out[0])
             assert torch.equal(x[r], keep[r])
-        # in place, twice in a row (counters must be back at zero)
+        # a second out-of-place call hands back a new tensor, not the first one's storage
+        out_b = tccl.double_tree_all_reduce(x, world=w)
+        torch.cuda.synchronize()
+        for r in range(W):
+            assert out_b[r].data_ptr() != out[r].data_ptr() and torch.equal(out_b[r], out[r])
+        # in place, twice in a row (the counters are running totals: nothing is reset in between)
         for _ in range(2):
             y = w.from_parts([p.clone() for p in keep])
             tccl.all_reduce(y, inplace=True, algo="tree", world=w)
@@ -284,10 +289,31 @@ def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb):
                 assert torch.equal(y[r], out[0])
     finally:
         w.config.tree_chunk_bytes = old
-    from tccl_b200.utils.lib import K
-    for r in range(W):
-        lo, hi = K["TCCL_FLAG_TREE_UP"], K["TCCL_FLAG_TILE"]
-        assert int(w.flags[r][lo:hi].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_double_tree_back_to_back_calls_of_changing_size(emu_worlds, W):
+    """No barrier separates two tree all-reduces: sizes, chunking and CTA counts change from call
+    to call while the ring and its counters carry on."""
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    old = w.config.tree_chunk_bytes
+    sizes = [(1 << 16, 4096), (4096, 1024), ((1 << 18) + 8, 1 << 22), (8, 1 << 22), (1 << 16, 256)]
+    try:
+        pending = []
+        for it in range(15):
+            n, chunk = sizes[it % len(sizes)]
+            w.config.tree_chunk_bytes = chunk
+            x = make_inputs(w, W, n, torch.float32, 3000 + 16 * it)
+            pending.append((tccl.double_tree_all_reduce(x, world=w), ref_sum(x)))
+        torch.cuda.synchronize()
+        w.check()
+        for out, ref in pending:
+            for r in range(W):
+                assert bool(((out[r].float() - ref).abs() <= ref.abs() * 1e-5 + 1e-5).all())
+    finally:
+        w.config.tree_chunk_bytes = old
 
 
 @pytest.mark.parametrize("W", [2, 3, 4, 8])
@@ -315,6 +341,32 @@ def test_all_reduce_push_small_messages(emu_worlds, W, dtype, n):
     torch.cuda.synchronize()
     for r in range(W):
         assert_close_to_sum(y[r], ref, dtype, W)
+
+
+@pytest.mark.parametrize("W", [2, 4, 8])
+def test_push_all_reduce_calls_of_alternating_size_and_grid(emu_worlds, W):
+    """64 KiB, 32 KiB and 1 KiB pushes in turn, 1000 calls with changing data and no host
+    synchronisation in between: the slot layout and the half in use must not depend on the
+    message size or on the grid, or a later call lands in bytes an earlier one still sums."""
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    sizes = [16384, 8192, 256]  # fp32 elements
+    data = {n: w.from_parts([torch.zeros(n) for _ in range(W)]) for n in sizes}
+    checks = []
+    for it in range(1000):
+        n = sizes[it % 3]
+        x = data[n]
+        for r in range(W):
+            x[r].fill_(float((it % 97) * (r + 1)))
+        out = tccl.all_reduce(x, algo="push_p2p", world=w)
+        if it % 40 in (37, 38, 39):
+            checks.append((out, float((it % 97) * W * (W + 1) // 2)))
+    torch.cuda.synchronize()
+    w.check()
+    for out, want in checks:
+        for r in range(W):
+            assert bool((out[r] == want).all())
 
 
 def test_large_all_reduce_into_ordinary_memory_uses_the_staged_two_shot(emu_worlds):

@@ -84,3 +84,22 @@ def test_protocol_is_race_free_under_thread_sanitizer(W):
     out = r.stdout + r.stderr
     assert "ThreadSanitizer" not in out, out[-3000:]
     assert r.returncode == 0, out[-2000:]
+
+
+def test_thread_sanitizer_flags_the_size_dependent_push_layout():
+    """The push all-reduce's slot layout must not depend on the message: with a slot size equal to
+    the message and the half taken from a CTA's own barrier epoch, calls of alternating size and
+    grid let a fast rank overwrite bytes a slow peer is still summing.  The model keeps that variant
+    so that this test can show ThreadSanitizer (or the sum check) catching it; the layout the kernel
+    uses runs clean in test_protocol_is_race_free_under_thread_sanitizer."""
+    import subprocess
+
+    from tccl_b200.utils import build as B
+
+    try:
+        exe = B.build_host_tsan()
+    except RuntimeError as e:
+        pytest.skip(str(e)[:200])
+    r = subprocess.run([str(exe), "push-broken-variant", "4"], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert "ThreadSanitizer: data race" in out or r.returncode != 0, out[-2000:]

@@ -7,18 +7,21 @@ from tccl_b200.ops._common import grid_for
 from tccl_b200.ops.collectives import choose_all_reduce_algo
 from tccl_b200.ops.fused import pack_gate_up
 from tccl_b200.ops.tree_allreduce import _tree_grid
+from tccl_b200.parallel.world import PlanCache, WorldBase
 from tccl_b200.utils.consts import K
 
 
-class StubWorld:
+class StubWorld(WorldBase):
     """The few attributes the selection code reads from a communicator."""
 
     def __init__(self, world_size, nvls, sms=148, **cfg):
-        self.world_size, self.has_nvls, self._sms = world_size, nvls, sms
+        self.world_size, self._nvls, self._sms = world_size, nvls, sms
         self.config = Config()
         for k, v in cfg.items():
             setattr(self.config, k, v)
         self.ll_bytes = 2 << 20
+
+    has_nvls = property(lambda self: self._nvls)
 
     def num_sms(self):
         return self._sms
@@ -58,16 +61,18 @@ def test_grid_is_a_function_of_size_and_shared_config_only():
     assert grid_for(StubWorld(1, False), 1 << 30, 512, 8) == 592  # one rank: a local copy, several CTAs per SM
 
 
-def test_tree_grid_keeps_chunks_large_enough():
+def test_tree_grid_fits_the_ring_and_scales_ctas_with_the_message():
     w = StubWorld(8, True)
+    slice_vecs = K["TCCL_TREE_SLICE_BYTES"] // 16
     k, vecs = _tree_grid(w, 1 << 30)
-    assert k == 32 and vecs * 16 == 4 << 20
+    assert k == 32 and vecs == k * slice_vecs          # large: every CTA moves a full ring slice per chunk
     k, vecs = _tree_grid(w, 1 << 20)
-    assert k == 8 and vecs * 16 >= k * 65536
+    assert k == 16 and vecs <= k * slice_vecs and (1 << 20) // 2 // (vecs * 16) >= 4  # >= 4 chunks per tree
     k, vecs = _tree_grid(w, 4096)
-    assert k == 1 and vecs >= 1
+    assert k == 1 and vecs >= 1                        # small: one CTA per role
     small = StubWorld(8, True, tree_chunk_bytes=1024)
-    assert _tree_grid(small, 1 << 20)[1] == 64  # small chunks on request
+    k, vecs = _tree_grid(small, 1 << 20)
+    assert vecs == 64 and vecs <= k * slice_vecs       # small chunks on request
 
 
 def test_pack_gate_up_layout():
@@ -78,3 +83,31 @@ def test_pack_gate_up_layout():
     assert p.shape == (2 * F, Kd)
     assert torch.equal(p[:128], gate[:128]) and torch.equal(p[128:256], up[:128])
     assert torch.equal(p[256:384], gate[128:]) and torch.equal(p[384:], up[128:])
+
+
+def test_plan_cache_is_bounded_and_evicts_the_least_recently_used():
+    c = PlanCache(3)
+    for k in "abc":
+        c.insert(k, k.upper())
+    assert c.lookup("a") == "A"          # refreshes "a"
+    c.insert("d", "D")                   # evicts "b", the least recently used
+    assert c.lookup("b") is None and len(c) == 3
+    assert [c.lookup(k) for k in "acd"] == ["A", "C", "D"]
+    c.clear()
+    assert len(c) == 0
+
+
+def test_plan_key_tells_a_strided_view_from_a_contiguous_tensor():
+    from tccl_b200.ops.collectives import _tkey
+
+    base = torch.zeros(64)
+    a, b = base[:16], base[:32:2]       # same address, element count and dtype; different layout
+    assert a.data_ptr() == b.data_ptr() and a.numel() == b.numel()
+    assert _tkey(a) != _tkey(b)
+    assert _tkey(a) == _tkey(base[:16])
+
+
+def test_push_slot_is_fixed_per_world_not_per_message():
+    w8, w3 = StubWorld(8, True), StubWorld(3, False)
+    assert w8.push_max_bytes() == (2 << 20) // 16
+    assert w3.push_max_bytes() % 16 == 0 and 2 * 3 * w3.push_max_bytes() <= w3.ll_bytes
