@@ -19,6 +19,13 @@ no bus; the all-reduce degenerates to a local copy and ``value`` is its
 algorithm bandwidth S / t (flagged in ``config.note``).  ``e2e`` repeats the
 measurement with, inside every timed step, a host-to-device copy of the step's
 input from pinned memory and a device-to-host read of a slice of the result.
+
+Beside the headline the line carries, measured in the same process on the same
+GPUs: ``nccl`` (``dist.all_reduce`` on a buffer of the same size, same steps),
+``secondary`` (reduce-scatter and all-gather at 256 MiB, all-reduce latency at
+8 KiB and double-tree all-reduce at 64 MiB, each for this library and for NCCL)
+and ``fused`` (the three tensor-parallel fused ops on Llama-3-8B MLP shapes
+against cuBLAS + NCCL + torch ops).  ``--no-extras`` skips those.
 """
 import argparse
 import json
@@ -31,6 +38,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 NUMEL = 256 * 1024 * 1024          # bf16 elements per rank = 512 MiB
+BLOCK = 1 << 20                    # the input is drawn block by block (see host_block)
+SAMPLE = 1 << 16                   # elements verified per window
 # Published numbers of the reference (8xH100, plot.ipynb block 1, 512 MiB): its Triton
 # all-reduce-like kernel 37.98 GB/s algorithm bandwidth; NCCL 203.1 GB/s.
 REF_TRITON_ALGBW = 37.9774
@@ -46,6 +55,7 @@ def parse():
     ap.add_argument("--numel", type=int, default=NUMEL)
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the nccl / secondary / fused measurements")
     return ap.parse_args()
 
 
@@ -65,6 +75,67 @@ def init_dist(n_gpus):
     return rank, local_rank, world
 
 
+def host_block(rank, b, m=BLOCK):
+    """Block ``b`` (BLOCK elements) of rank ``rank``'s input: N(0,1) from a generator seeded by
+    (2000 + rank, b), so that any window of any rank's data can be drawn again on any rank."""
+    import torch
+
+    g = torch.Generator(device="cpu").manual_seed((2000 + rank) * 1000003 + b)
+    return torch.randn(m, generator=g).to(torch.bfloat16)
+
+
+def fill_host(host, rank):
+    n = host.numel()
+    for b in range(-(-n // BLOCK)):
+        m = min(BLOCK, n - b * BLOCK)
+        host[b * BLOCK:b * BLOCK + m].copy_(host_block(rank, b)[:m])
+
+
+def sample_windows(n, W):
+    """One SAMPLE-element window at the start of every rank's slice of a two-shot reduction
+    (slice q starts at vector ceil(nvec / W) q) plus the last elements of the tensor."""
+    per = -(-(n // 8) // W) * 8
+    starts = sorted({min(q * per, max(0, n - SAMPLE)) for q in range(W)} | {max(0, n - SAMPLE)})
+    return [(s, min(SAMPLE, n - s)) for s in starts]
+
+
+def host_window(rank, start, length):
+    import torch
+
+    out = torch.empty(length, dtype=torch.bfloat16)
+    pos = start
+    while pos < start + length:
+        b, off = divmod(pos, BLOCK)
+        m = min(BLOCK - off, start + length - pos)
+        out[pos - start:pos - start + m] = host_block(rank, b)[off:off + m]
+        pos += m
+    return out
+
+
+def verify(result, n, W, impl):
+    """fp32 host sum of every rank's window against the device result."""
+    import torch
+
+    worst = 0.0
+    for start, length in sample_windows(n, W):
+        ref = torch.zeros(length, dtype=torch.float32)
+        prefix_mag = torch.zeros(length, dtype=torch.float32)
+        for r in range(W):
+            ref += host_window(r, start, length).float()
+            if r:
+                prefix_mag += ref.abs()
+        got = result[start:start + length].float().cpu()
+        if impl == "tccl_b200":
+            # an fp32 sum rounded once: to nearest (half an ulp) on the P2P paths, by the switch's
+            # conversion (within one ulp) on the NVLS paths
+            bound = ref.abs() * 2 ** -7 + 1e-5 * W
+        else:
+            # the reference adds in bf16, rank after rank: half an ulp of every running sum
+            bound = prefix_mag * 2 ** -8 * 1.01 + 1e-5 * W
+        worst = max(worst, float(((got - ref).abs() / bound).max()))
+    return worst <= 1.0, worst
+
+
 def timed_region(step, steps, warmup, sampler_rank0):
     """W untimed steps, then exactly K timed steps between barrier+synchronize
     pairs; returns (total ms as max over ranks, clocks summary or None)."""
@@ -76,8 +147,11 @@ def timed_region(step, steps, warmup, sampler_rank0):
     sampler = None
     if sampler_rank0:
         uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
-        sampler = ClockSampler(gpu_uuids=[uuid], period_ms=1.0)
+        sampler = ClockSampler(gpu_uuids=[uuid], period_ms=0.5)
         sampler.__enter__()
+        t_wait = time.perf_counter()
+        while not sampler.samples and time.perf_counter() - t_wait < 0.5:
+            time.sleep(0.001)  # the first NVML read takes a few milliseconds: longer than a short timed region
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
@@ -105,6 +179,146 @@ def timed_region(step, steps, warmup, sampler_rank0):
     return float(ms.item()), (sampler.summary() if sampler else None), wall_ms
 
 
+def p50_us(fn, iters, warmup, before=None):
+    import torch.distributed as dist
+
+    from tccl_b200.utils.timing import max_over_ranks, summarize, time_iters
+
+    return round(summarize(max_over_ranks(time_iters(fn, iters, warmup, before=before, sync=dist.barrier)))["p50_us"], 2)
+
+
+def secondary_metrics(tccl, w, x, y, W, n):
+    """Reduce-scatter / all-gather at 256 MiB, all-reduce latency at 8 KiB, double-tree
+    all-reduce at 64 MiB: this library next to NCCL, p50 of per-iteration device times."""
+    import torch
+    import torch.distributed as dist
+
+    dev = x.device
+    out = {}
+    half = n // 2                                  # 256 MiB of bf16
+    if W > 1 and half % (8 * W) == 0:
+        S = half * 2
+        o = torch.empty(half // W, dtype=torch.bfloat16, device=dev)
+        t_us = p50_us(lambda: tccl.reduce_scatter(x[:half], out=o), 20, 5)
+        n_us = p50_us(lambda: dist.reduce_scatter_tensor(o, x[:half]), 20, 5)
+        f = (W - 1) / W
+        out["reduce_scatter_256MiB"] = {"tccl_busbw_gbs": round(S * f / t_us / 1e3, 1), "nccl_busbw_gbs": round(S * f / n_us / 1e3, 1),
+                                        "tccl_p50_us": t_us, "nccl_p50_us": n_us}
+        shard = half // W
+        go = y[:half].view(W, shard)
+        t_us = p50_us(lambda: tccl.all_gather(x[:shard], out=go), 20, 5)
+        flat = torch.empty(half, dtype=torch.bfloat16, device=dev)
+        n_us = p50_us(lambda: dist.all_gather_into_tensor(flat, x[:shard]), 20, 5)
+        out["all_gather_256MiB_total"] = {"tccl_busbw_gbs": round(S * f / t_us / 1e3, 1), "nccl_busbw_gbs": round(S * f / n_us / 1e3, 1),
+                                          "tccl_p50_us": t_us, "nccl_p50_us": n_us}
+        del flat, o
+    # small-message latency, checked once before it is timed
+    xs = x[:4096]
+    o = torch.empty(4096, dtype=torch.bfloat16, device=dev)
+    tccl.all_reduce(xs, out=o)
+    torch.cuda.synchronize()
+    ref = torch.zeros(4096, dtype=torch.float32)
+    for r in range(W):
+        ref += host_window(r, 0, 4096).float()
+    small_ok = bool(((o.float().cpu() - ref).abs() <= ref.abs() * 2 ** -7 + 1e-5 * W).all())
+    lat = {"bytes": 8192, "tccl_p50_us": p50_us(lambda: tccl.all_reduce(xs, out=o), 200, 20), "verified": small_ok}
+    if W > 1:
+        z = o.clone()
+        lat["nccl_p50_us"] = p50_us(lambda: dist.all_reduce(z), 200, 20)
+    out["all_reduce_8KiB"] = lat
+    # double-tree all-reduce, 64 MiB, in place (the values grow from call to call: fp32 zeros)
+    m = 16 << 20
+    if n * 2 >= m * 4:
+        t32 = x.view(torch.float32)[:m]
+        keep = t32.clone()
+        t32.zero_()
+        t_us = p50_us(lambda: tccl.all_reduce(t32, inplace=True, algo="tree"), 10, 3)
+        t32.copy_(keep)
+        out["double_tree_all_reduce_64MiB"] = {"tccl_p50_us": t_us, "tccl_algbw_gbs": round(m * 4 / t_us / 1e3, 1)}
+        del keep
+    return out
+
+
+def fused_metrics(tccl, w, W):
+    """The three tensor-parallel fused ops on Llama-3-8B MLP shapes (4096 tokens, hidden 4096,
+    intermediate 14336 / W) against the unfused library sequence; each result checked first."""
+    import torch
+    import torch.distributed as dist
+
+    from tccl_b200.utils.timing import L2Flusher
+
+    T, H, I = 4096, 4096, 14336
+    if I % W or T % (128 * W) or (I // W) % 8:
+        return None
+    Il, rows = I // W, T // W
+    rank = w.rank
+    flush = L2Flusher("cuda")
+
+    def rnd(shape, seed, scale=1.0):
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+    res = {}
+    a_r, wd_r = rnd((T, Il), 4000 + rank), rnd((H, Il), 5000 + rank, 0.02)
+    o_buf = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+    part = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    tccl.gemm_reduce_scatter(a_r, wd_r, out=o_buf)
+    torch.matmul(a_r, wd_r.t(), out=part)
+    if W > 1:
+        chk = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
+        dist.reduce_scatter_tensor(chk, part)
+    else:
+        chk = part
+    torch.cuda.synchronize()
+    # against cuBLAS + NCCL (both round partials to bf16 before summing, in different orders)
+    ok = bool(((o_buf.float() - chk.float()).abs() <= chk.float().abs() * 2 ** -6 + 0.03 * W ** 0.5).all())
+
+    def unfused_a():
+        torch.matmul(a_r, wd_r.t(), out=part)
+        if W > 1:
+            dist.reduce_scatter_tensor(o_buf, part)
+    res["gemm_reduce_scatter"] = {"tccl_p50_us": p50_us(lambda: tccl.gemm_reduce_scatter(a_r, wd_r, out=o_buf), 30, 5, flush),
+                                  "cublas_nccl_p50_us": p50_us(unfused_a, 30, 5, flush), "verified": ok}
+    res["gemm_4096x4096x%d" % Il] = {"tccl_tcgen05_p50_us": p50_us(lambda: tccl.gemm_bf16(a_r, wd_r, out=part), 30, 5, flush),
+                                     "cublas_p50_us": p50_us(lambda: torch.matmul(a_r, wd_r.t(), out=part), 30, 5, flush)}
+    x_sh, wu_r = rnd((rows, H), 4000 + rank), rnd((Il, H), 6000 + rank, 0.02)
+    o2 = torch.empty(T, Il, dtype=torch.bfloat16, device="cuda")
+    gathered = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+
+    def unfused_b():
+        if W > 1:
+            dist.all_gather_into_tensor(gathered, x_sh)
+        else:
+            gathered.copy_(x_sh)
+        torch.matmul(gathered, wu_r.t(), out=o2)
+    unfused_b()
+    want = o2.clone()
+    _, a_full = tccl.all_gather_gemm(x_sh, wu_r, out=o2)
+    torch.cuda.synchronize()
+    ok = bool(torch.equal(a_full, gathered)) and bool(((o2.float() - want.float()).abs() <= want.float().abs() * 2 ** -7 + 2e-2).all())
+    res["all_gather_gemm"] = {"tccl_p50_us": p50_us(lambda: tccl.all_gather_gemm(x_sh, wu_r, out=o2), 30, 5, flush),
+                              "nccl_cublas_p50_us": p50_us(unfused_b, 30, 5, flush), "verified": ok}
+    xp = w.empty((T, H), torch.bfloat16)
+    xp.copy_(rnd((T, H), 4000 + rank))
+    bias, resid, wn = rnd((H,), 1, 0.5), rnd((T, H), 2), rnd((H,), 3)
+    tmp = xp.clone()
+
+    def unfused_c():
+        tmp.copy_(xp)
+        if W > 1:
+            dist.all_reduce(tmp)
+        return torch.nn.functional.rms_norm(tmp + bias + resid, (H,), wn, 1e-5)
+    yref = unfused_c().float()
+    yv = tccl.all_reduce_bias_residual_rmsnorm(xp, wn, bias, resid, eps=1e-5)
+    torch.cuda.synchronize()
+    ok = bool(((yv.float() - yref).abs() <= yref.abs() * 2 ** -5 + 3e-2).all())
+    res["allreduce_bias_residual_rmsnorm"] = {
+        "tccl_p50_us": p50_us(lambda: tccl.all_reduce_bias_residual_rmsnorm(xp, wn, bias, resid, eps=1e-5), 30, 5, flush),
+        "nccl_torch_p50_us": p50_us(unfused_c, 30, 5, flush), "verified": ok}
+    res["shapes"] = f"tokens {T}, hidden {H}, intermediate {I}/{W}, bf16; L2 flushed between iterations"
+    return res
+
+
 def main():
     a = parse()
     if a.impl == "reference":
@@ -119,15 +333,12 @@ def main():
     dev = torch.device("cuda", local_rank)
     n = a.numel
     S = n * 2
-    g = torch.Generator(device="cpu").manual_seed(2000 + rank)
     host = torch.empty(n, dtype=torch.bfloat16).pin_memory()
-    blk = 1 << 24
-    for off in range(0, n, blk):
-        m = min(blk, n - off)
-        host[off:off + m].copy_(torch.randn(m, generator=g).to(torch.bfloat16))
+    fill_host(host, rank)
     res_host = torch.empty(2048, dtype=torch.bfloat16).pin_memory()
 
     launches = [0]
+    tccl = w = None
     if a.impl == "tccl_b200":
         import tccl_b200 as tccl
 
@@ -181,18 +392,10 @@ def main():
         variant = "triton one_shot_all_reduce (reference)"
         status = None
 
-    # correctness of one call against an fp32 host sum on a sample of the tensor
+    # correctness of one call against an fp32 host sum: a window out of every rank's slice
     step()
     torch.cuda.synchronize()
-    sample = slice(0, 1 << 16)
-    refsum = torch.zeros(1 << 16, dtype=torch.float32)
-    for r in range(W):
-        gr = torch.Generator(device="cpu").manual_seed(2000 + r)
-        refsum += torch.randn(1 << 24 if n >= (1 << 24) else n, generator=gr)[sample].to(torch.bfloat16).float()
-    got = result()[sample].float().cpu()
-    # ours rounds an fp32 sum once; the reference adds in bf16, rank after rank
-    tol = refsum.abs() * 2 ** -7 + (0.02 if a.impl == "tccl_b200" else 0.08) * W
-    verified = bool(((got - refsum).abs() <= tol).all())
+    verified, worst = verify(result(), n, W, a.impl)
 
     # ---- device-timed region (kernel only) ----
     l0 = count()
@@ -216,23 +419,29 @@ def main():
             x.copy_(host, non_blocking=True)
             step()
             res_host.copy_(result()[:2048], non_blocking=True)
-        ems, _, _ = timed_region(e2e_step, max(3, a.steps // 2), 3, False)
+        ems, e2e_clocks, _ = timed_region(e2e_step, max(3, a.steps // 2), 3, rank == 0)
         et = ems / max(3, a.steps // 2) * 1e-3
         ealg = S / et / 1e9
         evalue = W * ealg * 2 * (W - 1) / W if W > 1 else ealg
         e2e = {"value": round(evalue, 3), "unit": "GB/s", "ms_per_step": round(et * 1e3, 4),
-               "h2d_bytes_per_step": S, "d2h_bytes_per_step": 4096}
+               "h2d_bytes_per_step": S, "d2h_bytes_per_step": 4096, "clocks": e2e_clocks}
 
-    # ---- small-message latency (8 KiB), p50 of per-iteration device times, max over ranks ----
-    lat = None
-    if a.impl == "tccl_b200":
-        from tccl_b200.utils.timing import max_over_ranks, summarize, time_iters
-
-        xs = x[:4096]
-        o = torch.empty(4096, dtype=torch.bfloat16, device=dev)
-        fn = lambda: tccl.all_reduce(xs, out=o)
-        lat_ms = max_over_ranks(time_iters(fn, 200, 20, sync=dist.barrier))
-        lat = {"bytes": 8192, "p50_us": round(summarize(lat_ms)["p50_us"], 2)}
+    nccl = secondary = fused = None
+    extras_error = None
+    if a.impl == "tccl_b200" and not a.no_extras:
+        try:
+            if W > 1:  # NCCL on a buffer of the same size, same steps and warm-up, same timing
+                y.zero_()  # the in-place sum of zeros stays finite over any number of steps
+                nms, _, _ = timed_region(lambda: dist.all_reduce(y), a.steps, a.warmup, False)
+                nt = nms / a.steps * 1e-3
+                nccl = {"ms_per_step": round(nt * 1e3, 4), "algbw_gbs": round(S / nt / 1e9, 3),
+                        "busbw_per_gpu_gbs": round(S / nt / 1e9 * 2 * (W - 1) / W, 3),
+                        "tccl_over_nccl": round(nt / t, 3)}
+            secondary = secondary_metrics(tccl, w, x, y, W, n)
+            x.copy_(host, non_blocking=True)
+            fused = fused_metrics(tccl, w, W)
+        except Exception as e:  # noqa: BLE001 - the headline stands without them
+            extras_error = f"{type(e).__name__}: {str(e)[:300]}"
 
     ok_status = True
     if status is not None:
@@ -250,29 +459,36 @@ def main():
             "scaling": "weak",
             "vs_baseline": round(busbw / (REF_TRITON_ALGBW * 2 * 7 / 8), 3) if W > 1 else None,
             "dtype": "bf16",
-            "data": "synthetic N(0,1), seed 2000+rank, random-init (no dataset)",
+            "data": "synthetic N(0,1), drawn per 1 Mi-element block with a generator seeded by (2000 + rank, block); "
+                    "random-init (no dataset)",
             "impl": a.impl,
+            "variant": variant,
             "algbw_gbs": round(algbw, 3),
             "busbw_per_gpu_gbs": round(busbw, 3),
             "vs_published_nccl_h100": round(algbw / REF_NCCL_ALGBW, 3),
             "verified": verified and ok_status,
+            "verify_worst_err_over_bound": round(worst, 3),
+            "verify_windows": len(sample_windows(n, W)),
             "gpu_launches": n_launch,
             "clocks": clocks,
             "e2e": e2e,
-            "small_message": lat,
+            "nccl": nccl,
+            "secondary": secondary,
+            "fused": fused,
             "config": {
                 "model": "none (collectives library): all-reduce, 268435456 bf16 elements per rank",
                 "global_batch": None,
                 "seq_len": None,
                 "message_bytes": S,
                 "parallelism": f"allreduce over {W} GPU(s), one process per GPU",
-                "variant": variant,
                 "l2": "message (512 MiB) is larger than L2 (126 MB); no flush needed",
                 "note": ("value = N x per-GPU bus bandwidth (S/t x 2(N-1)/N); with N=1 there is no bus and value is "
                          "the local copy's S/t. vs_baseline = per-GPU bus bandwidth / the reference's published "
                          "Triton all-reduce at 512 MiB on 8xH100 (37.98 GB/s algbw = 66.5 GB/s busbw)."),
             },
         }
+        if extras_error:
+            line["extras_error"] = extras_error
         print(json.dumps(line), flush=True)
     torch.cuda.synchronize()
     dist.barrier()

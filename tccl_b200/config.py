@@ -28,6 +28,11 @@ class Config:
     block: int = 512                  # threads per CTA of the data collectives
     nvls_ctas: int = 8                # CTAs of the NVLS two-shot all-reduce (the switch saturates early;
                                       # measured on 8xB200: 4-8 CTAs are best from 8 MiB up, 148 lose a third at 1 GiB)
+    pipe_min_bytes: int = 0           # all-reduce: from this size on use the pipelined two-shot (0 = never)
+    pipe_ctas: int = 16               # ... its CTAs,
+    pipe_reducers: int = 8            # ... warps (of 16 per CTA) that pull; the others push,
+    pipe_stages: int = 8              # ... shared-memory stages between the two groups,
+    pipe_unroll: int = 4              # ... and 16-byte vectors per reducer thread per stage (2, 4 or 8)
     stage_mb: int = 128               # symmetric staging area per rank
     disable_nvls: bool = False        # never pick a multimem variant
     nvls_barrier: bool = False        # barrier flavour used inside data kernels

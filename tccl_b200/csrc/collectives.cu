@@ -100,18 +100,6 @@ template <typename T> __device__ __forceinline__ char* vptr(void* base, uint64_t
   return reinterpret_cast<char*>(base) + vec * 16;
 }
 
-struct Entry {
-  uint64_t deadline;
-  bool nvls_bar;
-  __device__ __forceinline__ Entry(const tccl_comm& c, int flags, int bid)
-      : deadline(globaltimer() + c.timeout_ns), nvls_bar((flags & TCCL_F_NVLS_BARRIER) != 0) {
-    if (!(flags & TCCL_F_NO_ENTRY_BARRIER)) barrier_any(c, bid, deadline, nvls_bar);
-  }
-  __device__ __forceinline__ void exit(const tccl_comm& c, int flags, int bid) {
-    if (!(flags & TCCL_F_NO_EXIT_BARRIER)) barrier_any(c, bid, deadline, nvls_bar);
-  }
-};
-
 // Loop shape shared by the data kernels: in one sweep the grid covers one
 // contiguous window of nb * blockDim.x * U vectors (CTA b owns the b-th
 // blockDim.x * U slab of it, thread t the vectors t, t + blockDim.x, ... of the

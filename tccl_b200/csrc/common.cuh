@@ -266,6 +266,19 @@ __device__ __forceinline__ void barrier_any(const tccl_comm& c, int bid, uint64_
   else barrier_p2p(c, bid, deadline);
 }
 
+// entry / exit synchronisation shared by the data kernels
+struct Entry {
+  uint64_t deadline;
+  bool nvls_bar;
+  __device__ __forceinline__ Entry(const tccl_comm& c, int flags, int bid)
+      : deadline(globaltimer() + c.timeout_ns), nvls_bar((flags & TCCL_F_NVLS_BARRIER) != 0) {
+    if (!(flags & TCCL_F_NO_ENTRY_BARRIER)) barrier_any(c, bid, deadline, nvls_bar);
+  }
+  __device__ __forceinline__ void exit(const tccl_comm& c, int flags, int bid) {
+    if (!(flags & TCCL_F_NO_EXIT_BARRIER)) barrier_any(c, bid, deadline, nvls_bar);
+  }
+};
+
 // ---------------------------------------------------------- kernel scaffolding
 // Every collective is a struct `Op` with `using Args = ...` and
 // `static __device__ void run(const tccl_comm&, const Args&, int bid, int nblocks)`.

@@ -3,6 +3,8 @@
 // static device array instead of memory the caller (or anyone) allocates.
 #include <cooperative_groups.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "tccl_noalloc.h"
 
@@ -90,6 +92,7 @@ __global__ void __launch_bounds__(512, 1) noalloc_allreduce_kernel(const __grid_
 // ---------------------------------------------------------------- host side
 namespace {
 constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;             // first calls from several host threads may coincide
 uint32_t* g_scratch_addr[kMaxDevices];  // device address of g_noalloc_scratch, per device
 bool g_scratch_ready[kMaxDevices];
 
@@ -101,6 +104,7 @@ int scratch_for_current_device(uint32_t** ptr) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= kMaxDevices) return -TCCL_EINVAL;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
   if (!g_scratch_ready[dev]) {
     void* addr = nullptr;
     e = cudaGetSymbolAddress(&addr, g_noalloc_scratch);
@@ -124,6 +128,10 @@ extern "C" int tccl_allreduce_local_noalloc(const void* const* in, void* const* 
     p.in[r] = in[r];
     p.out[r] = out[r];
   }
+  // an output may not be one of the inputs: a rank stores its sums while the others still read
+  for (int r = 0; r < n_ranks; ++r)
+    for (int q = 0; q < n_ranks; ++q)
+      if (out[r] == in[q]) return -TCCL_EINVAL;
   p.numel = numel;
   p.timeout_ns = 2000000000ull;
   p.world = n_ranks;

@@ -109,12 +109,17 @@ typedef struct tccl_coll_args {
 #define TCCL_F_NO_EXIT_BARRIER 1 /* caller guarantees inputs stay untouched until peers are done */
 #define TCCL_F_NO_ENTRY_BARRIER 2
 #define TCCL_F_NVLS_BARRIER 4    /* use the multimem.red barrier flavour */
+/* pipelined two-shot all-reduce only; the same bits go into tccl_launch.meta */
+#define TCCL_F_PIPE_REDUCERS_SHIFT 8  /* 4 bits: warps (of 16) that pull; the others push */
+#define TCCL_F_PIPE_STAGES_SHIFT 12   /* 4 bits: shared-memory stages - 1 */
+#define TCCL_F_PIPE_UNROLL_SHIFT 16   /* 4 bits: vectors per reducer thread per stage (2, 4 or 8) */
 
 typedef struct tccl_launch {
   int32_t grid;    /* CTAs per rank */
   int32_t block;   /* threads per CTA */
   int32_t n_emu;   /* 0 = real, W = emulate W ranks on this GPU */
-  int32_t meta;    /* emulated mode only: tccl_dtype of the (device-resident) args */
+  int32_t meta;    /* bits 0-7: tccl_dtype of the args (read in emulated mode, where they are device-resident);
+                      bits 8..: kernel-specific shape bits (TCCL_F_PIPE_*) */
   void* stream;    /* cudaStream_t */
 } tccl_launch;
 
@@ -154,6 +159,9 @@ int tccl_allreduce_push_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_
 int tccl_allreduce_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_twoshot_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_twoshot_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+/* two-shot with reducer and broadcaster warps decoupled through a shared-memory ring (block = 512) */
+int tccl_allreduce_twoshot_pipe_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+int tccl_allreduce_twoshot_pipe_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_pull_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_push_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);

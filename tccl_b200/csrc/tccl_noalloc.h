@@ -26,12 +26,16 @@
  * with -TCCL_ESIZE and nothing is launched):
  *   n_ranks <= TCCL_NOALLOC_MAX_RANKS, ctas <= TCCL_NOALLOC_MAX_CTAS.
  * `numel` is not limited by the scratch.  Inputs and outputs must be 16-byte
- * aligned; `dtype` is a tccl_dtype.
+ * aligned; `dtype` is a tccl_dtype.  No output may be one of the inputs (every
+ * rank stores its sums while the others are still reading the inputs, so an
+ * in-place call would race): such a call is rejected with -TCCL_EINVAL; partially
+ * overlapping buffers are not detected and must be avoided by the caller.
  *
  * Set-up: the first call on each device looks up the device address of the
  * scratch array (cudaGetSymbolAddress, with that device current) and remembers
- * it.  Make that first call outside of any stream capture.  No call allocates or
- * frees memory, in this library or through another one.
+ * it.  Make that first call outside of any stream capture.  The look-up is
+ * guarded by a mutex, so first calls from several host threads are safe.  No call
+ * allocates or frees memory, in this library or through another one.
  *
  * Sharing: all calls on a device use the same scratch, and it keeps what the
  * previous call left there; each launch therefore clears the words that must

@@ -23,7 +23,7 @@ import torch
 
 from ..parallel.world import PlanCache, WorldBase  # noqa: F401  (PlanCache re-exported for tests)
 from ..utils import lib as L
-from ._common import check_sym_tensor, debug_log, dtype_code, get_world, grid_for
+from ._common import K, check_sym_tensor, debug_log, dtype_code, get_world, grid_for
 
 __all__ = [
     "all_reduce", "all_gather", "reduce_scatter",
@@ -38,7 +38,25 @@ _AR_KERNELS = {
     "oneshot_nvls": "tccl_allreduce_oneshot_nvls",
     "twoshot_p2p": "tccl_allreduce_twoshot_p2p",
     "twoshot_nvls": "tccl_allreduce_twoshot_nvls",
+    "twoshot_pipe_p2p": "tccl_allreduce_twoshot_pipe_p2p",
+    "twoshot_pipe_nvls": "tccl_allreduce_twoshot_pipe_nvls",
 }
+
+
+def pipe_bits(cfg, world_size: int, nvls: bool) -> int:
+    """Shape of the pipelined two-shot kernel as the bits its launcher and kernel read:
+    reducer warps (of 16), shared-memory stages, vectors per reducer thread per stage."""
+    nr = max(1, min(15, int(cfg.pipe_reducers)))
+    ur = int(cfg.pipe_unroll)
+    if ur not in (2, 4, 8):
+        raise ValueError("pipe_unroll must be 2, 4 or 8")
+    if not nvls and world_size * ur > 32:   # W loads per output vector: keep the registers in bounds
+        ur = 4 if world_size * 4 <= 32 else 2
+    stages = max(2, min(16, int(cfg.pipe_stages)))
+    while stages > 2 and stages * nr * 32 * ur * 16 > 200 * 1024:
+        stages -= 1
+    return ((nr << K["TCCL_F_PIPE_REDUCERS_SHIFT"]) | ((stages - 1) << K["TCCL_F_PIPE_STAGES_SHIFT"])
+            | (ur << K["TCCL_F_PIPE_UNROLL_SHIFT"]))
 
 
 _X, _OUT = "<the caller's input>", "<the caller's out>"  # Plan.result: hand back an argument of the call
@@ -149,7 +167,10 @@ def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -
         return "push_nvls" if nvls and world.world_size > 2 else "push_p2p"
     if not symmetric_dst or nbytes <= cfg.oneshot_max_bytes:
         return "oneshot_nvls" if nvls and world.world_size > 2 and nbytes <= 4 * cfg.oneshot_max_bytes else "oneshot_p2p"
-    return "twoshot_nvls" if nvls and world.world_size > 2 else "twoshot_p2p"
+    use_nvls = nvls and world.world_size > 2
+    if cfg.pipe_min_bytes and nbytes >= cfg.pipe_min_bytes:
+        return "twoshot_pipe_nvls" if use_nvls else "twoshot_pipe_p2p"
+    return "twoshot_nvls" if use_nvls else "twoshot_p2p"
 
 
 def all_reduce(x, out=None, *, inplace: bool = False, algo: str = "auto", world: Optional[WorldBase] = None,
@@ -283,6 +304,18 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
         a.mc_out = w.mc_ptr(dst)
         args[r] = a
     per_slice = -(-nvec // w.world_size)
+    if algo.startswith("twoshot_pipe"):
+        bits = pipe_bits(w.config, w.world_size, algo.endswith("nvls"))
+        for a in args.values():
+            a.flags |= bits
+        block = 512
+        nr = (bits >> K["TCCL_F_PIPE_REDUCERS_SHIFT"]) & 15
+        ur = (bits >> K["TCCL_F_PIPE_UNROLL_SHIFT"]) & 15
+        cap = w.config.max_ctas or w.config.pipe_ctas
+        grid = grid_for(w, per_slice, nr * 32, ur, cap=cap)
+        debug_log(w, f"all_reduce {nbytes} B -> {algo}, grid {grid} x {block}, pipe bits {bits:#x}")
+        return Plan(w, w.prepare(_AR_KERNELS[algo], args, grid, block, dt | bits), args,
+                    result=_X if inplace else _OUT)
     if algo == "twoshot_nvls":
         cap = w.config.nvls_ctas if not w.config.max_ctas else None
         grid = grid_for(w, per_slice, block, 8, cap=cap)

@@ -112,6 +112,33 @@ def test_all_reduce_twoshot_inplace(emu_worlds, W, dtype, n):
         assert torch.equal(x[r], x[0])
 
 
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 4, 4), (4, 8, 8), (12, 3, 2)])  # (reducer warps, stages, unroll)
+@pytest.mark.parametrize("n", [8, 65536 + 24, 3 * (1 << 20) + 5])
+def test_all_reduce_twoshot_pipelined(emu_worlds, W, dtype, shape, n):
+    """Reducer and broadcaster warps decoupled through a shared-memory ring: in place, twice in a
+    row (the second call finds the mbarriers re-initialised), for several shapes of the pipeline."""
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    old = (w.config.pipe_reducers, w.config.pipe_stages, w.config.pipe_unroll)
+    w.config.pipe_reducers, w.config.pipe_stages, w.config.pipe_unroll = shape
+    try:
+        for seed in (2000, 2100):
+            x = make_inputs(w, W, n, dtype, seed)
+            ref = ref_sum(x)
+            res = tccl.all_reduce(x, inplace=True, algo="twoshot_pipe_p2p", world=w)
+            torch.cuda.synchronize()
+            w.check()
+            assert res is x
+            for r in range(W):
+                assert_close_to_sum(x[r], ref, dtype, W)
+                assert torch.equal(x[r], x[0])
+    finally:
+        w.config.pipe_reducers, w.config.pipe_stages, w.config.pipe_unroll = old
+
+
 def test_all_reduce_twoshot_symmetric_out_keeps_input(emu_worlds):
     import tccl_b200 as tccl
 

@@ -62,6 +62,8 @@ def test_rejects_sizes_beyond_the_static_scratch():
 
     lib = L.lib()
     xs = [torch.zeros(64, device="cuda") for _ in range(9)]
-    assert _call(lib, xs, xs, L.DTYPES[torch.float32], 4) == -L.K["TCCL_ESIZE"]   # 9 ranks > 8
+    ys = [torch.zeros(64, device="cuda") for _ in range(9)]
+    assert _call(lib, xs, ys, L.DTYPES[torch.float32], 4) == -L.K["TCCL_ESIZE"]   # 9 ranks > 8
+    assert _call(lib, xs[:2], xs[:2], L.DTYPES[torch.float32], 4) == -L.K["TCCL_EINVAL"]  # in place: would race
     assert _call(lib, xs[:2], xs[2:4], L.DTYPES[torch.float32], 17) == -L.K["TCCL_ESIZE"]  # 17 CTAs > 16
     assert b"size" in lib.tccl_error_string(-L.K["TCCL_ESIZE"])
