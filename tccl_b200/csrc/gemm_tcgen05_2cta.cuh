@@ -110,8 +110,6 @@ struct Smem2 {
     epi[0] = p + (size_t)kStages2 * kStage2 + 256;
     epi[1] = epi[0] + kEpiChunkBytes;
   }
-  // what the single-CTA epilogues expect to find
-  __device__ SmemLayout as_epilogue_view() const;
 };
 
 // `half`: 0 = the full 256 columns of n tile nt, 1 / 2 = its left / right 128 columns

@@ -217,6 +217,9 @@ typedef struct tccl_gemm_args {
 } tccl_gemm_args;
 /* c = a * bt^T on this GPU; grid <= 0 picks one CTA per SM */
 int tccl_gemm_bf16(const tccl_gemm_args*, int grid, void* stream);
+/* same product on pairs of CTAs (tcgen05.mma.cta_group::2): 256 x 256 tiles, each CTA loads its own
+ * 128 rows of a and its own half of bt; the last partial wave is cut into 256 x 128 half tiles */
+int tccl_gemm_bf16_pair(const tccl_gemm_args*, int grid, void* stream);
 
 /* ---- fused GEMM -> reduce-scatter (rows scattered over the ranks) ---------- */
 typedef struct tccl_gemm_rs_args {
