@@ -1,0 +1,310 @@
+// All-gather -> GEMM in ONE kernel on the CTA-pair mainloop
+// (gemm_tcgen05_2cta.cuh):
+//   out_r[M, N_r] = gather_src(A_src[M/W, K]) * Bt_r[N_r, K]^T
+//
+// What differs from the single-CTA form (ag_gemm.cu):
+//  * No CTA is set aside to move data.  EVERY CTA opens as a data mover: for each
+//    128-row tile of this rank's shard it stores its 1/grid share into the
+//    gathered buffer of every rank (one multimem.st per vector through the switch
+//    when NVLS is there, else one posted store per peer), and the mover that
+//    completes a row tile raises that tile's flag on every rank.  With the whole
+//    GPU issuing, the shard is on the wire within a few microseconds instead of
+//    trickling out of 8 CTAs for the whole length of the kernel.  Then the CTAs
+//    turn into GEMM pairs.
+//  * 256 x 256 tiles on pairs of SMs (tcgen05.mma.cta_group::2).  A pair starts
+//    on the rank's own rows, straight from the shard, and goes on with the remote
+//    row tiles in the order they arrive; each CTA's TMA producer waits for the
+//    flag of its own 128 rows and then loads them from LOCAL memory (the gathered
+//    buffer) — a tensor map never covers a peer's memory.
+//  * No entry barrier when the gathered buffer is the library's own: it has two
+//    halves that alternate from call to call (TCCL_LOCAL_AG_SEQ).  A rank reaches
+//    call n+2 only after its call n+1 consumed every peer's rows of call n+1,
+//    i.e. after every peer has finished call n and stopped reading the half that
+//    is being overwritten.  A caller-provided buffer keeps the barrier.
+#include "gemm_host.cuh"
+#include "gemm_tcgen05_2cta.cuh"
+
+namespace tccl {
+namespace gemm2 {
+
+struct alignas(64) AgGemmPairParams {
+  CUtensorMap map_a_shard, map_a_full[2], map_b;
+  Shape shp;
+  const char* a_shard;
+  char* a_full[TCCL_MAX_WORLD];  // every rank's gathered buffer (half 0)
+  char* mc_a_full;               // its multicast alias, or null
+  uint64_t half_bytes;           // distance to half 1 (0: one buffer only, entry barrier)
+  __nv_bfloat16* out;
+  int lda_shard, lda_full, ldo;
+  int tiles_n, tiles_m_per_rank;
+  int swiglu;
+};
+
+struct AgGemmPairPolicy {
+  const tccl_comm* c;
+  const AgGemmPairParams* p;
+  int pair, npairs;
+  uint32_t epoch;
+  int parity;
+
+  __device__ __forceinline__ bool tile(int i, int& mt, int& nt, int& half) const {
+    const int t = pair + i * npairs;
+    const int tm2 = p->tiles_m_per_rank / 2, tn = p->tiles_n, W = c->world;
+    const int own = tm2 * tn;
+    half = 0;
+    if (t >= W * own) return false;
+    if (t < own) {  // own rows first: no waiting
+      mt = c->rank * p->tiles_m_per_rank + 2 * (t / tn);
+      nt = t % tn;
+      return true;
+    }
+    // remote rows in arrival order: pair-row by pair-row, peers from the next rank on
+    const int u = t - own;
+    const int per_rt = (W - 1) * tn;
+    const int rt2 = u / per_rt, v = u - rt2 * per_rt;
+    int src = c->rank + 1 + v / tn;
+    if (src >= W) src -= W;
+    mt = src * p->tiles_m_per_rank + 2 * rt2;
+    nt = v % tn;
+    return true;
+  }
+  __device__ __forceinline__ const CUtensorMap* map_b(int) const { return &p->map_b; }
+  __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
+  __device__ __forceinline__ void between_tiles(int, int, const Abort&) const {}
+  __device__ __forceinline__ bool before_load(int mt, int, const Abort& ab) const {
+    const int src = mt / p->tiles_m_per_rank;
+    if (src == c->rank) return true;
+    const int rt = mt - src * p->tiles_m_per_rank;
+    const bool ok = wait_reach(c->flags[c->rank] + TCCL_FLAG_AG + src * TCCL_MAX_ROW_TILES + rt, epoch, *c,
+                               ab.deadline, src, TCCL_W_TILE);
+    if (!ok) *ab.flag = 1;
+    fence_proxy_async();  // rows written through the generic proxy are read by TMA next
+    return ok;
+  }
+  __device__ __forceinline__ void a_tile(int mt, const CUtensorMap*& map, int& y) const {
+    const int src = mt / p->tiles_m_per_rank;
+    if (src == c->rank) {
+      map = &p->map_a_shard;
+      y = (mt - src * p->tiles_m_per_rank) * 128;
+    } else {
+      map = &p->map_a_full[parity];
+      y = mt * 128;
+    }
+  }
+  __device__ __forceinline__ bool epilogue(int mt, int nt, int, int, uint32_t taddr, int quad, int lane, const Abort&,
+                                           const Smem2&) const {
+    const int row = mt * 128 + quad * 32 + lane;
+    __nv_bfloat16* crow = p->out + (size_t)row * p->ldo;
+    if (p->swiglu) {
+      // every 256-wide tile holds 128 gate columns followed by the 128 matching up columns
+#pragma unroll 1
+      for (int cg = 0; cg < BN2 / 64; ++cg) {
+        uint32_t g[32], u[32];
+        tmem_ld_32x32(taddr + cg * 32, g);
+        tmem_ld_32x32(taddr + BN2 / 2 + cg * 32, u);
+        tmem_ld_wait();
+        const int col0 = nt * (BN2 / 2) + cg * 32;
+        if (row < p->shp.M) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 < p->shp.N / 2) {
+              uint32_t o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float gv = __uint_as_float(g[v * 8 + e]), uv = __uint_as_float(u[v * 8 + e]);
+                o[e] = __float_as_uint(gv / (1.f + __expf(-gv)) * uv);
+              }
+              st_local(crow + col0 + v * 8, pack8_bf16(o));
+            }
+          }
+        }
+      }
+      return true;
+    }
+#pragma unroll 1
+    for (int cg = 0; cg < BN2 / 32; ++cg) {
+      uint32_t r[32];
+      tmem_ld_32x32(taddr + cg * 32, r);
+      tmem_ld_wait();
+      const int col0 = nt * BN2 + cg * 32;
+      if (row < p->shp.M) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          if (col0 + v * 8 < p->shp.N) st_local(crow + col0 + v * 8, pack8_bf16(r + v * 8));
+      }
+    }
+    return true;
+  }
+};
+
+// every CTA moves its share of every row tile of the shard; the last one per row tile publishes it
+__device__ void ag_push_all(const tccl_comm& c, const AgGemmPairParams& p, int bid, int nb, uint32_t epoch, int parity) {
+  __shared__ int s_last;
+  const int W = c.world, me = c.rank;
+  const int vec_per_row = p.shp.K / 8;
+  const int rows_per_rank = p.tiles_m_per_rank * 128;
+  const uint64_t hoff = (uint64_t)parity * p.half_bytes;
+  const uint32_t nvec = 128u * (uint32_t)vec_per_row;
+  const uint32_t per = (nvec + nb - 1) / nb;
+  const uint32_t lo = min(per * (uint32_t)bid, nvec), hi = min(lo + per, nvec);
+  for (int rt = 0; rt < p.tiles_m_per_rank; ++rt) {
+    constexpr int U = 4;
+    for (uint32_t i0 = lo + threadIdx.x; i0 < hi; i0 += U * blockDim.x) {
+      Vec16 v[U];
+      size_t dst[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t i = i0 + u * blockDim.x;
+        if (i < hi) {
+          const int row = rt * 128 + i / vec_per_row, col = (i % vec_per_row) * 8;
+          v[u] = ld_peer(p.a_shard + ((size_t)row * p.lda_shard + col) * 2);
+          dst[u] = hoff + ((size_t)(me * rows_per_rank + row) * p.lda_full + col) * 2;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * blockDim.x < hi) {
+          if (p.mc_a_full) {
+            multimem_st(p.mc_a_full + dst[u], v[u]);
+          } else {
+            for (int q = 0; q < W; ++q) st_peer(p.a_full[q] + dst[u], v[u]);
+          }
+        }
+      }
+    }
+    __syncthreads();  // this CTA's share of the row tile is stored
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_AGCNT + rt, 1u);
+      s_last = (done == (uint32_t)nb - 1u);
+      if (s_last) {
+        c.local[TCCL_LOCAL_AGCNT + rt] = 0u;
+        fence_acq_rel_sys();
+      }
+    }
+    __syncthreads();
+    if (s_last && (int)threadIdx.x < W)
+      st_release_sys(c.flags[threadIdx.x] + TCCL_FLAG_AG + me * TCCL_MAX_ROW_TILES + rt, epoch);
+  }
+}
+
+__device__ __forceinline__ void ag_gemm_pair_body(const tccl_comm& c, const AgGemmPairParams& p, int bid, int nb) {
+  const uint32_t epoch = c.local[TCCL_LOCAL_TILE_EPOCH] + 1u;
+  const int parity = p.half_bytes ? (int)(c.local[TCCL_LOCAL_AG_SEQ] & 1u) : 0;
+  if (!p.half_bytes) {
+    // one buffer only: every rank must be done reading it from the previous call
+    barrier_p2p(c, bid, globaltimer() + c.timeout_ns);
+  }
+  ag_push_all(c, p, bid, nb, epoch, parity);  // also with one rank: the gathered buffer is part of the result
+  AgGemmPairPolicy pol;
+  pol.c = &c;
+  pol.p = &p;
+  pol.pair = bid >> 1;
+  pol.npairs = nb >> 1;
+  pol.epoch = epoch;
+  pol.parity = parity;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&p.map_a_shard);
+    tma_prefetch_desc(&p.map_a_full[parity]);
+    tma_prefetch_desc(&p.map_b);
+  }
+  run_mainloop2(p.shp, pol, &c, c.timeout_ns);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_SCHED, 1u);
+    if (done == (uint32_t)nb - 1u) {
+      c.local[TCCL_LOCAL_SCHED] = 0u;
+      c.local[TCCL_LOCAL_AG_SEQ] += 1u;
+      c.local[TCCL_LOCAL_TILE_EPOCH] = epoch;
+    }
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+ag_gemm_pair_kernel(const __grid_constant__ tccl_comm comm, const __grid_constant__ AgGemmPairParams p) {
+  ag_gemm_pair_body(comm, p, blockIdx.x, gridDim.x);
+}
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+ag_gemm_pair_kernel_emu(const tccl_comm* comms, const AgGemmPairParams* ps) {
+  ag_gemm_pair_body(comms[blockIdx.y], ps[blockIdx.y], blockIdx.x, gridDim.x);
+}
+
+static int fill_params(AgGemmPairParams* p, const tccl_ag_gemm_args* g, int world, int rank, uint64_t half_bytes) {
+  if (g->m <= 0 || g->n <= 0 || g->k <= 0) return -TCCL_EINVAL;
+  if ((g->lda_shard % 8) || (g->lda_full % 8) || (g->ldb % 8) || (g->ldo % 8) || (g->k % 8) || (g->n % 8))
+    return -TCCL_EALIGN;
+  if (g->m % (world * 256)) return -TCCL_ESIZE;  // whole 256-row pair tiles per rank
+  if (((uintptr_t)g->a_shard | (uintptr_t)g->bt | (uintptr_t)g->out | (uintptr_t)g->a_full[rank] | half_bytes) & 15)
+    return -TCCL_EALIGN;
+  const int rows = g->m / world;
+  int rc = make_tmap_bf16_kmajor(&p->map_a_shard, g->a_shard, rows, g->k, g->lda_shard, 128);
+  if (rc) return rc;
+  for (int h = 0; h < 2; ++h) {
+    const char* base = reinterpret_cast<const char*>(g->a_full[rank]) + (h ? half_bytes : 0);
+    rc = make_tmap_bf16_kmajor(&p->map_a_full[h], base, g->m, g->k, g->lda_full, 128);
+    if (rc) return rc;
+  }
+  rc = make_tmap_bf16_kmajor(&p->map_b, g->bt, g->n, g->k, g->ldb, 128);
+  if (rc) return rc;
+  p->shp = Shape{g->m, g->n, g->k};
+  p->a_shard = reinterpret_cast<const char*>(g->a_shard);
+  for (int q = 0; q < TCCL_MAX_WORLD; ++q) p->a_full[q] = reinterpret_cast<char*>(g->a_full[q]);
+  p->mc_a_full = reinterpret_cast<char*>(g->mc_a_full);
+  p->half_bytes = half_bytes;
+  p->out = reinterpret_cast<__nv_bfloat16*>(g->out);
+  p->lda_shard = g->lda_shard;
+  p->lda_full = g->lda_full;
+  p->ldo = g->ldo;
+  p->tiles_n = (g->n + BN2 - 1) / BN2;
+  p->tiles_m_per_rank = rows / 128;
+  p->swiglu = g->swiglu;
+  if (g->swiglu && (g->n % BN2)) return -TCCL_ESIZE;  // whole gate|up tiles only
+  if (p->tiles_m_per_rank > TCCL_MAX_ROW_TILES) return -TCCL_ESIZE;
+  return 0;
+}
+
+}  // namespace gemm2
+}  // namespace tccl
+
+using namespace tccl::gemm;
+using namespace tccl::gemm2;
+
+extern "C" uint64_t tccl_ag_gemm_pair_param_bytes(void) { return sizeof(AgGemmPairParams); }
+
+// Same calling convention as tccl_allgather_gemm (comm_ctas and lsu_movers of the arguments are not
+// used: every CTA moves data first).  `half_bytes`: distance in bytes from a_full[q] to the second
+// half of every rank's gathered buffer, or 0 when there is only one buffer (then the kernel opens
+// with a barrier).  l->grid must be even.
+extern "C" int tccl_allgather_gemm_pair(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,
+                                        uint64_t half_bytes, const tccl_launch* l) {
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(l->stream);
+  if (l->grid < 2 || (l->grid & 1)) return -TCCL_EINVAL;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(ag_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem2);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(ag_gemm_pair_kernel_emu, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmem2);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  if (l->n_emu == 0) {
+    AgGemmPairParams p;
+    int rc = fill_params(&p, args, comm->world, comm->rank, half_bytes);
+    if (rc) return rc;
+    ag_gemm_pair_kernel<<<l->grid, kThreads, kSmem2, s>>>(*comm, p);
+    return (int)cudaGetLastError();
+  }
+  const int W = l->n_emu;
+  if (W < 1 || W > TCCL_MAX_WORLD || !dev_params || ((uintptr_t)dev_params & 63)) return -TCCL_EINVAL;
+  AgGemmPairParams ps[TCCL_MAX_WORLD];
+  for (int r = 0; r < W; ++r) {
+    int rc = fill_params(&ps[r], &args[r], W, r, half_bytes);
+    if (rc) return rc;
+  }
+  cudaError_t e = cudaMemcpyAsync(dev_params, ps, sizeof(AgGemmPairParams) * W, cudaMemcpyHostToDevice, s);
+  if (e != cudaSuccess) return (int)e;
+  const AgGemmPairParams* dps = reinterpret_cast<const AgGemmPairParams*>(dev_params);
+  return launch_pairs_emulated((const void*)ag_gemm_pair_kernel_emu, l->grid, W, kSmem2, s, (const void*)&comm,
+                               (const void*)&dps);
+}

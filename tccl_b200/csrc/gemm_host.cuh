@@ -42,5 +42,39 @@ inline int make_tmap_bf16_kmajor(CUtensorMap* map, const void* base, int rows, i
   return r == CUDA_SUCCESS ? 0 : -TCCL_EINVAL;
 }
 
+// Emulated ranks of a kernel built on CTA pairs (compile-time cluster dimensions 2 x 1 x 1): one
+// launch of `grid` x `world` CTAs.  The ranks' CTAs wait on one another, so all of them must be
+// resident together: a cooperative launch guarantees that or fails cleanly; where the runtime does
+// not take a cooperative launch of a cluster kernel, the launch goes ahead only if the occupancy
+// query says that every cluster fits at once.
+inline int launch_pairs_emulated(const void* fn, int grid, int world, size_t smem, cudaStream_t s, const void* arg0,
+                                 const void* arg1) {
+  void* kargs[2] = {const_cast<void*>(arg0), const_cast<void*>(arg1)};
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid, world), dim3(256), kargs, smem, s);
+  if (e == cudaSuccess) return 0;
+  if (e != cudaErrorInvalidValue && e != cudaErrorNotSupported && e != cudaErrorInvalidConfiguration &&
+      e != cudaErrorLaunchFailure)
+    return (int)e;
+  if (e == cudaErrorLaunchFailure) return (int)e;
+  (void)cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, world);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  e = cudaOccupancyMaxActiveClusters(&clusters, fn, &cfg);
+  if (e != cudaSuccess) return (int)e;
+  if (clusters * 2 < grid * world) return (int)cudaErrorCooperativeLaunchTooLarge;
+  return (int)cudaLaunchKernelExC(&cfg, fn, kargs);
+}
+
 }  // namespace gemm
 }  // namespace tccl

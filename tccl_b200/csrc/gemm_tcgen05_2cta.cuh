@@ -121,6 +121,7 @@ struct Smem2 {
 //   epilogue(mt, nt, col0, ncols, taddr, quad, lane, ab, sm)
 //                                          -> 4 epilogue warps of each CTA; columns [col0, col0 + ncols) of
 //                                             n tile nt start at tensor-memory address taddr
+//   between_tiles(quad, lane, ab)          -> epilogue warps, after a tile's accumulator has been released
 //   epilogue_finish(quad, lane, ab)
 template <class Policy>
 __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* comm, uint64_t timeout_ns) {
@@ -230,6 +231,7 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
       ok = pol.epilogue(mt, nt, half == 2 ? 128 : 0, half ? 128 : 256, taddr, quad, lane, ab, sm);
       tc_fence_before();
       mbar_arrive_cluster(leader_tempty0 + (uint32_t)acc * 8);  // the leader's tmem_empty[acc], from either CTA
+      if (ok) pol.between_tiles(quad, lane, ab);                // the accumulator is released: time for side work
     }
     pol.epilogue_finish(quad, lane, ab);
   }

@@ -50,7 +50,10 @@ extern "C" {
 #define TCCL_LOCAL_PUSH_SEQ (TCCL_LOCAL_AGCNT + TCCL_MAX_ROW_TILES) /* push all-reduce calls completed (slot parity) */
 #define TCCL_LOCAL_PUSH_DONE (TCCL_LOCAL_PUSH_SEQ + 1)           /* CTAs of the running push all-reduce that are done */
 #define TCCL_LOCAL_TREE_SEQ (TCCL_LOCAL_PUSH_DONE + 1)           /* [role][cta]: chunks this pipeline moved in earlier calls */
-#define TCCL_LOCAL_WORDS (TCCL_LOCAL_TREE_SEQ + 4 * TCCL_TREE_MAX_CTAS)
+#define TCCL_LOCAL_RS_SEQ (TCCL_LOCAL_TREE_SEQ + 4 * TCCL_TREE_MAX_CTAS) /* pair GEMM -> RS calls completed (staging half) */
+#define TCCL_LOCAL_RS_NEXT (TCCL_LOCAL_RS_SEQ + 1)               /* pair GEMM -> RS: next reduction unit to hand out */
+#define TCCL_LOCAL_AG_SEQ (TCCL_LOCAL_RS_NEXT + 1)               /* pair AG -> GEMM calls completed (gather buffer half) */
+#define TCCL_LOCAL_WORDS (TCCL_LOCAL_AG_SEQ + 1)
 
 enum tccl_status_word {
   TCCL_ST_CODE = 0,   /* 0 = ok, else tccl_error */
@@ -239,6 +242,16 @@ uint64_t tccl_gemm_rs_param_bytes(void);
 int tccl_gemm_reduce_scatter(const tccl_comm* comm, const tccl_gemm_rs_args* args, void* dev_params,
                              uint64_t stage_bytes, const tccl_launch* l);
 
+/* Same product on CTA pairs (tcgen05.mma.cta_group::2), tiles interleaved over the owners so that the
+ * reduction overlaps the mainloop, and no entry barrier: the staging area is used in two alternating
+ * halves.  m % (world * 256) == 0; l->grid even.  TCCL_RS_SYNC_ENTRY in l->meta asks for an entry
+ * barrier (needed when the previous user of the staging area was another kernel). */
+#define TCCL_RS_SYNC_ENTRY 256
+uint64_t tccl_gemm_rs_pair_stage_bytes(int m, int n, int world);
+uint64_t tccl_gemm_rs_pair_param_bytes(void);
+int tccl_gemm_reduce_scatter_pair(const tccl_comm* comm, const tccl_gemm_rs_args* args, void* dev_params,
+                                  uint64_t stage_bytes, const tccl_launch* l);
+
 /* ---- fused all-gather -> GEMM (rows gathered over the ranks) -------------- */
 typedef struct tccl_ag_gemm_args {
   const void* a_shard;              /* this rank's [m / world, k] rows, k contiguous */
@@ -258,6 +271,14 @@ uint64_t tccl_ag_gemm_param_bytes(void);
 /* same calling convention as tccl_gemm_reduce_scatter */
 int tccl_allgather_gemm(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,
                         const tccl_launch* l);
+
+/* Same product on CTA pairs (tcgen05.mma.cta_group::2); every CTA moves its share of the shard first
+ * (comm_ctas / lsu_movers are not used).  m % (world * 256) == 0; l->grid even.  `half_bytes`: distance
+ * from a_full[q] to the second half of every rank's gathered buffer — the halves alternate from call to
+ * call and no entry barrier is needed — or 0 for a single buffer (the kernel then opens with a barrier). */
+uint64_t tccl_ag_gemm_pair_param_bytes(void);
+int tccl_allgather_gemm_pair(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,
+                             uint64_t half_bytes, const tccl_launch* l);
 
 #ifdef __cplusplus
 }

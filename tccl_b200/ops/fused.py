@@ -38,14 +38,22 @@ def _trace_ptr(w: WorldBase, trace, r: int, grid: int) -> int:
     return t.data_ptr()
 
 
-def _gemm_ctas(w: WorldBase) -> int:
+def _gemm_ctas(w: WorldBase, pairs: bool = False) -> int:
     n = w.config.max_ctas or w.num_sms()
     if w.plans is None:  # emulated ranks share one GPU and each CTA takes a whole SM
         n = max(1, w.num_sms() // w.world_size)
-    return n
+    return max(2, n & ~1) if pairs else n
 
 
-def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBase] = None):
+def _stage_handoff(w: WorldBase, user: str) -> bool:
+    """Whether a kernel that runs without an entry barrier must take one this time: the staging
+    area was last used by a different kernel (every rank sees the same sequence of calls)."""
+    last = w.__dict__.get("_stage_user")
+    w.__dict__["_stage_user"] = user
+    return last != user
+
+
+def gemm_reduce_scatter(a, bt, out=None, *, trace=None, variant: str = "auto", world: Optional[WorldBase] = None):
     """``out_r = rows r of sum_ranks (a_rank @ bt_rank.T)`` — tensor-parallel
     down-projection fused with the reduce-scatter over token rows.
 
@@ -53,7 +61,11 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBas
     dimension), ``bt``: its ``[N, K_r]`` weight slice (``nn.Linear`` layout), both
     bf16.  Returns this rank's ``[M / W, N]`` rows.  ``M % (128 W) == 0`` and
     ``N % 256 == 0``.  Inputs and output are ordinary tensors; the partial tiles
-    travel through the communicator's symmetric staging area."""
+    travel through the communicator's symmetric staging area.
+
+    ``variant``: ``"pair"`` = 256 x 256 tiles on pairs of SMs, the reduction overlapped with the
+    mainloop, no entry barrier (needs ``M % (256 W) == 0`` and twice the staging space);
+    ``"single"`` = 128 x 256 single-CTA tiles; ``"auto"`` = pair when the shape allows."""
     w = get_world(world)
     W = w.world_size
     As, Bs = _locals(w, a), _locals(w, bt)
@@ -67,15 +79,28 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBas
     if M % (W * 128) or N % 256 or Kr % 8:
         raise ValueError(f"need M % {W * 128} == 0, N % 256 == 0, K % 8 == 0 (got M={M}, N={N}, K={Kr})")
     lib = L.lib()
-    lib.tccl_gemm_rs_stage_bytes.restype = C.c_uint64
-    lib.tccl_gemm_rs_param_bytes.restype = C.c_uint64
-    need = lib.tccl_gemm_rs_stage_bytes(M, N, W)
+    for f in ("tccl_gemm_rs_stage_bytes", "tccl_gemm_rs_param_bytes", "tccl_gemm_rs_pair_stage_bytes",
+              "tccl_gemm_rs_pair_param_bytes"):
+        getattr(lib, f).restype = C.c_uint64
     stage_bytes = (w.config.stage_mb << 20) - w.ll_bytes
+    if variant not in ("auto", "pair", "single"):
+        raise ValueError("variant must be 'auto', 'pair' or 'single'")
+    pair_ok = M % (W * 256) == 0 and lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) <= stage_bytes and trace is None
+    if variant == "pair" and not pair_ok:
+        raise ValueError(f"the pair kernel needs M % {W * 256} == 0 and "
+                         f"{lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) >> 20} MiB of staging area (and no trace)")
+    pair = pair_ok and variant != "single"
+    need = lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) if pair else lib.tccl_gemm_rs_stage_bytes(M, N, W)
     if need > stage_bytes:
         raise ValueError(f"staging area too small: need {need >> 20} MiB, have {w.config.stage_mb} MiB "
                          "(raise TCCL_STAGE_MB)")
     outs = {}
-    grid = _gemm_ctas(w)
+    grid = _gemm_ctas(w, pair)
+    meta = 0
+    if pair:
+        meta = K["TCCL_RS_SYNC_ENTRY"] if _stage_handoff(w, "gemm_rs_pair") else 0
+    else:
+        _stage_handoff(w, "gemm_rs")
     Os = _locals(w, out) if out is not None else None
     arr = (L.GemmRsArgs * len(w.local_ranks))()
     for i, r in enumerate(w.local_ranks):
@@ -87,18 +112,18 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBas
         arr[i] = L.GemmRsArgs(ar.data_ptr(), br.data_ptr(), o.data_ptr(), M, N, Kr, ar.stride(0), br.stride(0),
                               o.stride(0), _trace_ptr(w, trace, r, grid))
     stream = torch.cuda.current_stream(a0.device).cuda_stream
-    fn = lib.tccl_gemm_reduce_scatter
+    fn = lib.tccl_gemm_reduce_scatter_pair if pair else lib.tccl_gemm_reduce_scatter
     if w.plans is not None:
-        l = L.Launch(grid, 256, 0, 0, C.c_void_p(stream))
+        l = L.Launch(grid, 256, 0, meta, C.c_void_p(stream))
         rc = fn(C.byref(w.comm), C.byref(arr[0]), None, C.c_uint64(stage_bytes), C.byref(l))
     else:
-        pb = int(lib.tccl_gemm_rs_param_bytes())
+        pb = int(lib.tccl_gemm_rs_pair_param_bytes() if pair else lib.tccl_gemm_rs_param_bytes())
         scratch = torch.empty(pb * W + 64, dtype=torch.uint8, device=a0.device)
         base = (scratch.data_ptr() + 63) & ~63
         w._keep.append(scratch)
-        l = L.Launch(grid, 256, W, 0, C.c_void_p(stream))
+        l = L.Launch(grid, 256, W, meta, C.c_void_p(stream))
         rc = fn(C.c_void_p(w.comms_dev.data_ptr()), arr, C.c_void_p(base), C.c_uint64(stage_bytes), C.byref(l))
-    L.check(rc, "tccl_gemm_reduce_scatter")
+    L.check(rc, "tccl_gemm_reduce_scatter_pair" if pair else "tccl_gemm_reduce_scatter")
     w.launches += 1
     if out is not None:
         return out
@@ -106,7 +131,7 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, world: Optional[WorldBas
 
 
 def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, swiglu: bool = False, trace=None,
-                    lsu_movers: bool = False, world: Optional[WorldBase] = None):
+                    lsu_movers: bool = False, variant: str = "auto", world: Optional[WorldBase] = None):
     """``out_r = all_gather(a_shard) @ bt_r.T`` — tensor-parallel up-projection
     fused with the all-gather of the token rows.
 
@@ -118,7 +143,14 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
 
     ``swiglu=True`` fuses the gated activation into the epilogue: ``bt`` must be
     packed by :func:`pack_gate_up` (every 256-row block = 128 gate rows, then the
-    128 matching up rows) and ``out`` is ``[M, N_r / 2] = silu(gate) * up``."""
+    128 matching up rows) and ``out`` is ``[M, N_r / 2] = silu(gate) * up``.
+
+    ``variant``: ``"pair"`` = 256 x 256 tiles on pairs of SMs, every CTA moves its share of the
+    shard before it computes (needs ``M % (256 W) == 0``); ``"single"`` = 128 x 256 single-CTA
+    tiles with ``comm_ctas`` dedicated data movers; ``"auto"`` = pair when the shape allows.  When
+    the pair kernel allocates the gathered buffer itself it keeps two of them and alternates (so it
+    needs no barrier on entry): the returned ``a_full`` is the one this call filled, and it stays
+    valid until the call after the next one."""
     w = get_world(world)
     W = w.world_size
     As, Bs = _locals(w, a_shard), _locals(w, bt)
@@ -134,16 +166,38 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
     if swiglu and N % 256:
         raise ValueError("swiglu needs N % 256 == 0 (whole gate|up tiles)")
     n_out = N // 2 if swiglu else N
+    if variant not in ("auto", "pair", "single"):
+        raise ValueError("variant must be 'auto', 'pair' or 'single'")
+    pair_ok = rows % 256 == 0 and trace is None
+    if variant == "pair" and not pair_ok:
+        raise ValueError("the pair kernel needs (M / W) % 256 == 0 (and no trace)")
+    pair = pair_ok and variant != "single"
+    half_bytes = 0
+    ret_full = a_full
+    seq = 0
+    if pair:  # mirrors the device's count of pair calls, which picks the half (see reset())
+        seq = w.__dict__.get("_ag_seq", 0)
+        w.__dict__["_ag_seq"] = seq + 1
     if a_full is None:
         cache = w.__dict__.setdefault("_ag_buffers", {})
-        a_full = cache.get((M, Kd))
+        key = (M, Kd, pair)
+        a_full = cache.get(key)
         if a_full is None:
-            a_full = cache[(M, Kd)] = w.empty((M, Kd), torch.bfloat16)
+            a_full = cache[key] = w.empty((2, M, Kd) if pair else (M, Kd), torch.bfloat16)
+        ret_full = a_full
+        if pair:
+            half_bytes = M * Kd * 2
+            if w.plans is not None:
+                ret_full = a_full[seq & 1]
+            else:
+                from ..parallel.emu import EmuTensor
+                ret_full = EmuTensor([t[seq & 1] for t in a_full.parts])
     full_ptrs = w.peer_ptrs(a_full)
     mc = w.mc_ptr(a_full)
     lib = L.lib()
     lib.tccl_ag_gemm_param_bytes.restype = C.c_uint64
-    grid = _gemm_ctas(w)
+    lib.tccl_ag_gemm_pair_param_bytes.restype = C.c_uint64
+    grid = _gemm_ctas(w, pair)
     if comm_ctas <= 0:
         # Few data movers: every mover CTA is an SM the GEMM does not get, and 8 movers
         # with 8 vectors per thread in flight already fill the link (measured on 8xB200,
@@ -175,21 +229,26 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.lsu_movers = 1 if lsu_movers else 0
         arr[i] = g
     stream = torch.cuda.current_stream(a0.device).cuda_stream
-    fn = lib.tccl_allgather_gemm
+    if pair:
+        fn = lib.tccl_allgather_gemm_pair
+        extra = (C.c_uint64(half_bytes),)
+    else:
+        fn = lib.tccl_allgather_gemm
+        extra = ()
     if w.plans is not None:
         l = L.Launch(grid, 256, 0, 0, C.c_void_p(stream))
-        rc = fn(C.byref(w.comm), C.byref(arr[0]), None, C.byref(l))
+        rc = fn(C.byref(w.comm), C.byref(arr[0]), None, *extra, C.byref(l))
     else:
-        pb = int(lib.tccl_ag_gemm_param_bytes())
+        pb = int(lib.tccl_ag_gemm_pair_param_bytes() if pair else lib.tccl_ag_gemm_param_bytes())
         scratch = torch.empty(pb * W + 64, dtype=torch.uint8, device=a0.device)
         base = (scratch.data_ptr() + 63) & ~63
         w._keep.append(scratch)
         l = L.Launch(grid, 256, W, 0, C.c_void_p(stream))
-        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), arr, C.c_void_p(base), C.byref(l))
-    L.check(rc, "tccl_allgather_gemm")
+        rc = fn(C.c_void_p(w.comms_dev.data_ptr()), arr, C.c_void_p(base), *extra, C.byref(l))
+    L.check(rc, "tccl_allgather_gemm_pair" if pair else "tccl_allgather_gemm")
     w.launches += 1
     res = out if out is not None else ([outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]])
-    return res, a_full
+    return res, ret_full
 
 
 def all_reduce_bias_residual_rmsnorm(x, weight, bias=None, residual=None, eps: float = 1e-5, out=None,

@@ -200,6 +200,8 @@ class EmuWorld(WorldBase):
         torch.cuda.synchronize(self.device)
         for t in self.flags + self.local_states:
             t.zero_()
+        for k in ("_ag_seq", "_stage_user"):  # host-side mirrors of device state
+            self.__dict__.pop(k, None)
         torch.cuda.synchronize(self.device)
 
     def set_timeout_ms(self, ms: float) -> None:

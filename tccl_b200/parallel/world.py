@@ -318,6 +318,8 @@ class RealWorld(WorldBase):
         self._dist.barrier(self.group)
         self.workspace[: self._flag_bytes].zero_()
         self.local_state.zero_()
+        for k in ("_ag_seq", "_stage_user"):  # host-side mirrors of device state
+            self.__dict__.pop(k, None)
         torch.cuda.synchronize(self.device)
         self._dist.barrier(self.group)
 

@@ -11,16 +11,20 @@ def _rand(shape, seed, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).cuda()
 
 
+@pytest.mark.parametrize("variant", ["single", "pair"])
 @pytest.mark.parametrize("W,M,N,K", [(1, 256, 256, 128), (2, 256, 256, 64), (2, 512, 512, 1792), (4, 1024, 512, 448),
-                                     (8, 1024, 256, 224), (4, 2048, 1024, 1792)])
-def test_gemm_reduce_scatter(emu_worlds, W, M, N, K):
+                                     (8, 1024, 256, 224), (4, 2048, 1024, 1792), (8, 2048, 512, 224),
+                                     (2, 1024, 768, 8), (3, 768, 256, 72)])
+def test_gemm_reduce_scatter(emu_worlds, W, M, N, K, variant):
     import tccl_b200 as tccl
 
+    if variant == "pair" and M % (256 * W):
+        pytest.skip("the pair kernel needs whole 256-row tiles per rank")
     w = emu_worlds(W)
     a = [_rand((M, K), 4000 + r) for r in range(W)]
     bt = [_rand((N, K), 5000 + r, 0.02) for r in range(W)]
-    for rep in range(2):  # twice: the tile epochs must advance together
-        outs = tccl.gemm_reduce_scatter(a, bt, world=w)
+    for rep in range(3):  # several times: epochs advance together and the staging halves alternate
+        outs = tccl.gemm_reduce_scatter(a, bt, variant=variant, world=w)
         torch.cuda.synchronize()
         w.check()
         ref = sum(a[r].float() @ bt[r].float().t() for r in range(W))
@@ -34,18 +38,21 @@ def test_gemm_reduce_scatter(emu_worlds, W, M, N, K):
             assert bool((err <= bound).all()), f"rank {r}: max err {err.max().item()} ratio {(err / bound).max().item()}"
 
 
+@pytest.mark.parametrize("variant", ["single", "pair"])
 @pytest.mark.parametrize("W,M,N,K", [(1, 256, 256, 128), (2, 256, 512, 64), (2, 1024, 1792, 512), (4, 1024, 264, 448),
-                                     (8, 1024, 256, 256), (4, 2048, 1792, 1024)])
-def test_all_gather_gemm(emu_worlds, W, M, N, K):
+                                     (8, 1024, 256, 256), (4, 2048, 1792, 1024), (8, 2048, 264, 256), (3, 768, 520, 72)])
+def test_all_gather_gemm(emu_worlds, W, M, N, K, variant):
     import tccl_b200 as tccl
 
+    if variant == "pair" and M % (256 * W):
+        pytest.skip("the pair kernel needs whole 256-row tiles per rank")
     w = emu_worlds(W)
     rows = M // W
     shards = [_rand((rows, K), 4000 + r) for r in range(W)]
     bt = [_rand((N, K), 5000 + r, 0.02) for r in range(W)]
     a_all = torch.cat(shards).float()
-    for rep in range(2):
-        outs, a_full = tccl.all_gather_gemm(shards, bt, world=w)
+    for rep in range(3):
+        outs, a_full = tccl.all_gather_gemm(shards, bt, variant=variant, world=w)
         torch.cuda.synchronize()
         w.check()
         for r in range(W):
@@ -83,7 +90,28 @@ def test_all_reduce_bias_residual_rmsnorm(emu_worlds, W, T, H, with_res):
         assert torch.equal(y[r], y[0])
 
 
-def test_all_gather_gemm_swiglu(emu_worlds):
+def test_fused_kernels_take_turns_on_the_staging_area(emu_worlds):
+    """Pair and single-CTA GEMM -> reduce-scatter calls mixed with shape changes: the pair kernel runs
+    without an entry barrier only after a call of its own kind; a change of user brings the barrier back."""
+    import tccl_b200 as tccl
+
+    W = 2
+    w = emu_worlds(W)
+    for M, N, K, variant in [(512, 256, 64, "pair"), (512, 256, 64, "pair"), (256, 256, 64, "single"),
+                             (1024, 512, 128, "pair"), (512, 256, 64, "pair"), (512, 512, 64, "single"), (512, 256, 64, "pair")]:
+        a = [_rand((M, K), 4000 + r + M) for r in range(W)]
+        bt = [_rand((N, K), 5000 + r + N, 0.02) for r in range(W)]
+        outs = tccl.gemm_reduce_scatter(a, bt, variant=variant, world=w)
+        torch.cuda.synchronize()
+        w.check()
+        ref = sum(a[r].float() @ bt[r].float().t() for r in range(W))
+        for r in range(W):
+            exp = ref[r * (M // W):(r + 1) * (M // W)]
+            assert bool(((outs[r].float() - exp).abs() <= exp.abs() * 2 ** -7 + 1e-2).all())
+
+
+@pytest.mark.parametrize("variant", ["single", "pair"])
+def test_all_gather_gemm_swiglu(emu_worlds, variant):
     import tccl_b200 as tccl
     from tccl_b200.ops.fused import pack_gate_up
 
@@ -93,7 +121,7 @@ def test_all_gather_gemm_swiglu(emu_worlds):
     gate = [_rand((F, K), 20 + r, 0.05) for r in range(W)]
     up = [_rand((F, K), 30 + r, 0.05) for r in range(W)]
     packed = [pack_gate_up(gate[r], up[r]) for r in range(W)]
-    outs, _ = tccl.all_gather_gemm(shards, packed, swiglu=True, world=w)
+    outs, _ = tccl.all_gather_gemm(shards, packed, swiglu=True, variant=variant, world=w)
     torch.cuda.synchronize()
     w.check()
     a = torch.cat(shards).float()
