@@ -82,7 +82,7 @@ def main():
     acts = [rnd((T, Il), 4000 + r) for r in range(W)] if T * Il * W <= (1 << 28) else None
     a_r = rnd((T, Il), 4000 + rank)
     wd_r = rnd((H, Il), 5000 + rank, 0.02)
-    out = tccl.gemm_reduce_scatter(a_r, wd_r)
+    out = tccl.gemm_reduce_scatter(a_r, wd_r, variant="single")
     torch.cuda.synchronize()
     ref = torch.zeros(rows, H, dtype=torch.float32, device="cuda")
     for r in range(W):
@@ -94,8 +94,14 @@ def main():
     flops = 2.0 * T * H * Il
     link = (W - 1) / W * T * H * 2
     o_buf = torch.empty(rows, H, dtype=torch.bfloat16, device="cuda")
-    report("gemm_reduce_scatter", "tccl_b200 fused", timeit(lambda: tccl.gemm_reduce_scatter(a_r, wd_r, out=o_buf)),
-           flops, link, ok_a)
+    for variant in ("pair", "single"):
+        if variant == "pair" and T % (256 * W):
+            continue
+        chk = tccl.gemm_reduce_scatter(a_r, wd_r, variant=variant)
+        torch.cuda.synchronize()
+        ok_v = ok_a and bool(torch.equal(chk, out) or ((chk.float() - out.float()).abs() <= out.float().abs() * 2 ** -7 + 1e-2).all())
+        report("gemm_reduce_scatter", f"tccl_b200 fused ({variant})",
+               timeit(lambda: tccl.gemm_reduce_scatter(a_r, wd_r, out=o_buf, variant=variant)), flops, link, ok_v)
     part = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
 
     def unfused_a():
@@ -103,12 +109,14 @@ def main():
         dist.reduce_scatter_tensor(o_buf, part)
     report("gemm_reduce_scatter", "cublas + nccl", timeit(unfused_a), flops, link, True)
     report("gemm_only", "cublas", timeit(lambda: torch.matmul(a_r, wd_r.t(), out=part)), flops, 0, True)
-    report("gemm_only", "tccl_b200 tcgen05", timeit(lambda: tccl.gemm_bf16(a_r, wd_r, out=part)), flops, 0, True)
+    report("gemm_only", "tccl_b200 tcgen05 (pair)", timeit(lambda: tccl.gemm_bf16(a_r, wd_r, out=part)), flops, 0, True)
+    report("gemm_only", "tccl_b200 tcgen05 (single)",
+           timeit(lambda: tccl.gemm_bf16(a_r, wd_r, out=part, variant="single")), flops, 0, True)
 
     # ---------------- (b) all-gather -> GEMM
     x_sh = rnd((rows, H), 4000 + rank)
     wu_r = rnd((Il, H), 6000 + rank, 0.02)
-    res, a_full = tccl.all_gather_gemm(x_sh, wu_r)
+    res, a_full = tccl.all_gather_gemm(x_sh, wu_r, variant="single")
     torch.cuda.synchronize()
     x_all = torch.cat([rnd((rows, H), 4000 + r) for r in range(W)])
     ref = x_all.float() @ wu_r.float().t()
@@ -118,9 +126,16 @@ def main():
     flops = 2.0 * T * H * Il
     link = (W - 1) * rows * H * 2
     o2 = torch.empty(T, Il, dtype=torch.bfloat16, device="cuda")
+    if rows % 256 == 0:
+        res_p, a_full_p = tccl.all_gather_gemm(x_sh, wu_r, variant="pair")
+        torch.cuda.synchronize()
+        ok_p = bool(torch.equal(a_full_p, x_all)) and bool(torch.equal(res_p, res) or (
+            (res_p.float() - res.float()).abs() <= res.float().abs() * 2 ** -7 + 1e-2).all())
+        report("all_gather_gemm", "tccl_b200 fused (pair)",
+               timeit(lambda: tccl.all_gather_gemm(x_sh, wu_r, out=o2, variant="pair")), flops, link, ok_p)
     for cc in [int(v) for v in a.ag_comm_ctas.split(",")]:
-        report("all_gather_gemm", f"tccl_b200 fused (movers={cc or 'auto'})",
-               timeit(lambda: tccl.all_gather_gemm(x_sh, wu_r, out=o2, comm_ctas=cc)), flops, link, ok_b)
+        report("all_gather_gemm", f"tccl_b200 fused (single, movers={cc or 'auto'})",
+               timeit(lambda: tccl.all_gather_gemm(x_sh, wu_r, out=o2, comm_ctas=cc, variant="single")), flops, link, ok_b)
     gathered = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
 
     def unfused_b():

@@ -3,14 +3,15 @@
 //   out_r[M, N_r] = gather_src(A_src[M/W, K]) * Bt_r[N_r, K]^T
 //
 // What differs from the single-CTA form (ag_gemm.cu):
-//  * No CTA is set aside to move data.  EVERY CTA opens as a data mover: for each
-//    128-row tile of this rank's shard it stores its 1/grid share into the
-//    gathered buffer of every rank (one multimem.st per vector through the switch
-//    when NVLS is there, else one posted store per peer), and the mover that
-//    completes a row tile raises that tile's flag on every rank.  With the whole
-//    GPU issuing, the shard is on the wire within a few microseconds instead of
-//    trickling out of 8 CTAs for the whole length of the kernel.  Then the CTAs
-//    turn into GEMM pairs.
+//  * No CTA is set aside to move data.  The four epilogue warps of EVERY CTA open
+//    as data movers while the producer and MMA warps already compute on the
+//    rank's own rows: in two batches of row tiles each CTA stores its 1/grid
+//    share of the shard into the gathered buffer of every rank (one multimem.st
+//    per vector through the switch when NVLS is there, else one posted store per
+//    peer), and the CTA that completes a batch raises the flags of its row tiles
+//    on every rank.  With the whole GPU issuing, the shard is on the wire within
+//    microseconds instead of trickling out of 8 CTAs for the length of the kernel,
+//    and no SM is lost to the GEMM.
 //  * 256 x 256 tiles on pairs of SMs (tcgen05.mma.cta_group::2).  A pair starts
 //    on the rank's own rows, straight from the shard, and goes on with the remote
 //    row tiles in the order they arrive; each CTA's TMA producer waits for the
@@ -46,6 +47,7 @@ struct AgGemmPairPolicy {
   int pair, npairs;
   uint32_t epoch;
   int parity;
+  int* s_last;  // shared: whether this CTA completed a batch of the data-mover phase
 
   __device__ __forceinline__ bool tile(int i, int& mt, int& nt, int& half) const {
     const int t = pair + i * npairs;
@@ -71,6 +73,70 @@ struct AgGemmPairPolicy {
   __device__ __forceinline__ const CUtensorMap* map_b(int) const { return &p->map_b; }
   __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
   __device__ __forceinline__ void between_tiles(int, int, const Abort&) const {}
+
+  // The data-mover phase, run by the four epilogue warps of EVERY CTA while the producer and MMA
+  // warps already work on the rank's own rows (the first accumulator is tens of microseconds
+  // away).  The shard's row tiles go out in two batches; in each, CTA b stores its 1/grid share of
+  // every row tile into the gathered buffer of every rank, and the CTA that completes a batch
+  // raises the flags of its row tiles on every rank.  One system-scope fence per batch: a fence
+  // per row tile would cost a switch round trip each and hold back the whole kernel.
+  __device__ void epilogue_begin(int quad, int lane, const Abort&) const {
+    const int W = c->world, me = c->rank, nb = 2 * npairs, bid = blockIdx.x;
+    const int t = quad * 32 + lane;
+    const int vec_per_row = p->shp.K / 8;
+    const int rows_per_rank = p->tiles_m_per_rank * 128;
+    const uint64_t hoff = (uint64_t)parity * p->half_bytes;
+    const uint32_t nvec = 128u * (uint32_t)vec_per_row;
+    const uint32_t per = (nvec + nb - 1) / nb;
+    const uint32_t lo = min(per * (uint32_t)bid, nvec), hi = min(lo + per, nvec);
+    const int nbatch = p->tiles_m_per_rank >= 2 ? 2 : 1;
+    for (int b = 0; b < nbatch; ++b) {
+      const int rt0 = b * p->tiles_m_per_rank / nbatch, rt1 = (b + 1) * p->tiles_m_per_rank / nbatch;
+      for (int rt = rt0; rt < rt1; ++rt) {
+        constexpr int U = 8;
+        for (uint32_t i0 = lo + t; i0 < hi; i0 += U * 128) {
+          Vec16 v[U];
+          size_t dst[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * 128;
+            if (i < hi) {
+              const int row = rt * 128 + i / vec_per_row, col = (i % vec_per_row) * 8;
+              v[u] = ld_peer(p->a_shard + ((size_t)row * p->lda_shard + col) * 2);
+              dst[u] = hoff + ((size_t)(me * rows_per_rank + row) * p->lda_full + col) * 2;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (i0 + u * 128 < hi) {
+              if (p->mc_a_full) {
+                multimem_st(p->mc_a_full + dst[u], v[u]);
+              } else {
+                for (int q = 0; q < W; ++q) st_peer(p->a_full[q] + dst[u], v[u]);
+              }
+            }
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // this CTA's share of the batch is stored
+      if (t == 0) {
+        fence_acq_rel_sys();
+        const uint32_t done = atomicAdd(c->local + TCCL_LOCAL_AGCNT + b, 1u);
+        *s_last = (done == (uint32_t)nb - 1u);
+        if (*s_last) {
+          c->local[TCCL_LOCAL_AGCNT + b] = 0u;
+          fence_acq_rel_sys();
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*reinterpret_cast<volatile int*>(s_last)) {
+        for (int k = t; k < W * (rt1 - rt0); k += 128)
+          st_release_sys(c->flags[k % W] + TCCL_FLAG_AG + me * TCCL_MAX_ROW_TILES + rt0 + k / W, epoch);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // s_last is rewritten by the next batch
+    }
+  }
+
   __device__ __forceinline__ bool before_load(int mt, int, const Abort& ab) const {
     const int src = mt / p->tiles_m_per_rank;
     if (src == c->rank) return true;
@@ -137,57 +203,6 @@ struct AgGemmPairPolicy {
   }
 };
 
-// every CTA moves its share of every row tile of the shard; the last one per row tile publishes it
-__device__ void ag_push_all(const tccl_comm& c, const AgGemmPairParams& p, int bid, int nb, uint32_t epoch, int parity) {
-  __shared__ int s_last;
-  const int W = c.world, me = c.rank;
-  const int vec_per_row = p.shp.K / 8;
-  const int rows_per_rank = p.tiles_m_per_rank * 128;
-  const uint64_t hoff = (uint64_t)parity * p.half_bytes;
-  const uint32_t nvec = 128u * (uint32_t)vec_per_row;
-  const uint32_t per = (nvec + nb - 1) / nb;
-  const uint32_t lo = min(per * (uint32_t)bid, nvec), hi = min(lo + per, nvec);
-  for (int rt = 0; rt < p.tiles_m_per_rank; ++rt) {
-    constexpr int U = 4;
-    for (uint32_t i0 = lo + threadIdx.x; i0 < hi; i0 += U * blockDim.x) {
-      Vec16 v[U];
-      size_t dst[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const uint32_t i = i0 + u * blockDim.x;
-        if (i < hi) {
-          const int row = rt * 128 + i / vec_per_row, col = (i % vec_per_row) * 8;
-          v[u] = ld_peer(p.a_shard + ((size_t)row * p.lda_shard + col) * 2);
-          dst[u] = hoff + ((size_t)(me * rows_per_rank + row) * p.lda_full + col) * 2;
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i0 + u * blockDim.x < hi) {
-          if (p.mc_a_full) {
-            multimem_st(p.mc_a_full + dst[u], v[u]);
-          } else {
-            for (int q = 0; q < W; ++q) st_peer(p.a_full[q] + dst[u], v[u]);
-          }
-        }
-      }
-    }
-    __syncthreads();  // this CTA's share of the row tile is stored
-    if (threadIdx.x == 0) {
-      fence_acq_rel_sys();
-      const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_AGCNT + rt, 1u);
-      s_last = (done == (uint32_t)nb - 1u);
-      if (s_last) {
-        c.local[TCCL_LOCAL_AGCNT + rt] = 0u;
-        fence_acq_rel_sys();
-      }
-    }
-    __syncthreads();
-    if (s_last && (int)threadIdx.x < W)
-      st_release_sys(c.flags[threadIdx.x] + TCCL_FLAG_AG + me * TCCL_MAX_ROW_TILES + rt, epoch);
-  }
-}
-
 __device__ __forceinline__ void ag_gemm_pair_body(const tccl_comm& c, const AgGemmPairParams& p, int bid, int nb) {
   const uint32_t epoch = c.local[TCCL_LOCAL_TILE_EPOCH] + 1u;
   const int parity = p.half_bytes ? (int)(c.local[TCCL_LOCAL_AG_SEQ] & 1u) : 0;
@@ -195,8 +210,9 @@ __device__ __forceinline__ void ag_gemm_pair_body(const tccl_comm& c, const AgGe
     // one buffer only: every rank must be done reading it from the previous call
     barrier_p2p(c, bid, globaltimer() + c.timeout_ns);
   }
-  ag_push_all(c, p, bid, nb, epoch, parity);  // also with one rank: the gathered buffer is part of the result
+  __shared__ int s_last;
   AgGemmPairPolicy pol;
+  pol.s_last = &s_last;
   pol.c = &c;
   pol.p = &p;
   pol.pair = bid >> 1;

@@ -71,6 +71,7 @@ struct PlainPolicy2 {
   }
   __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
   __device__ __forceinline__ void between_tiles(int, int, const Abort&) const {}
+  __device__ __forceinline__ void epilogue_begin(int, int, const Abort&) const {}
   __device__ __forceinline__ bool epilogue(int mt, int nt, int col0, int ncols, uint32_t taddr, int quad, int lane,
                                            const Abort&, const Smem2&) const {
     const int row = mt * 128 + quad * 32 + lane;

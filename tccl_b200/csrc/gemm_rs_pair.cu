@@ -196,6 +196,7 @@ struct GemmRsPairPolicy {
   }
   // the copy engine has the tile and the accumulator is free again: use the wait for reduction work
   __device__ __forceinline__ void between_tiles(int quad, int lane, const Abort&) { try_reduce(quad, lane, 2); }
+  __device__ __forceinline__ void epilogue_begin(int, int, const Abort&) const {}
 };
 
 __device__ __forceinline__ void gemm_rs_pair_body(const tccl_comm& c, const GemmRsPairParams& p, int bid, int nb) {

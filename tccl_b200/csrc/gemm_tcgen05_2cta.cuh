@@ -121,6 +121,7 @@ struct Smem2 {
 //   epilogue(mt, nt, col0, ncols, taddr, quad, lane, ab, sm)
 //                                          -> 4 epilogue warps of each CTA; columns [col0, col0 + ncols) of
 //                                             n tile nt start at tensor-memory address taddr
+//   epilogue_begin(quad, lane, ab)         -> epilogue warps, once, before they wait for the first accumulator
 //   between_tiles(quad, lane, ab)          -> epilogue warps, after a tile's accumulator has been released
 //   epilogue_finish(quad, lane, ab)
 template <class Policy>
@@ -221,6 +222,7 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
     const uint32_t leader_tempty0 = mapa(smem_u32(sm.tmem_empty), 0);
     bool ok = true;
     int mt, nt, half;
+    pol.epilogue_begin(quad, lane, ab);  // the first accumulator is a whole tile away: time for side work
     for (int i = 0; ok && pol.tile(i, mt, nt, half); ++i) {
       mt += (int)cta;
       const int acc = i & 1;
