@@ -63,7 +63,7 @@ def __getattr__(name):
     ops = importlib.import_module(".ops", __name__)
     if hasattr(ops, name):
         return getattr(ops, name)
-    for mod in ("ops.tree_allreduce", "ops.fused", "ops.gemm"):
+    for mod in ("ops.tree_allreduce", "ops.fused", "ops.gemm", "ops.quantized"):
         try:
             m = importlib.import_module("." + mod, __name__)
         except ImportError:

@@ -43,10 +43,12 @@ class Config:
     staged_max_bytes: int = 1 << 30       # ... up to this message size (the buffer is kept per size and dtype)
     tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
     tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
+    tree_ll_max_bytes: int = 256 * 1024   # double-tree: up to here the flags travel inside the data lines
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
     plan_cache_size: int = 512            # bound launches kept per communicator (least recently used go first)
     debug: bool = False
+    debug_shrink_extent: int = 0          # test hook of the TCCL_DEBUG_CHECKS build: claim this many bytes less input
 
     @classmethod
     def from_env(cls) -> "Config":

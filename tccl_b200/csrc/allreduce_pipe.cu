@@ -88,7 +88,7 @@ struct AllReduceTwoShotPipe {
 #pragma unroll
           for (int u = 0; u < UR; ++u) {
             const uint64_t i = base + u * NR + t;
-            if (i < end) v[u] = MultimemOps<T>::ld_reduce(reinterpret_cast<const char*>(a.mc_in) + i * 16);
+            if (i < end && TCCL_VIN(c, a, i)) v[u] = MultimemOps<T>::ld_reduce(reinterpret_cast<const char*>(a.mc_in) + i * 16);
           }
 #pragma unroll
           for (int u = 0; u < UR; ++u) gemm::st_shared_v4(st + (size_t)(u * NR + t) * 16, v[u]);
@@ -100,7 +100,7 @@ struct AllReduceTwoShotPipe {
 #pragma unroll
               for (int u = 0; u < UR; ++u) {
                 const uint64_t i = base + u * NR + t;
-                if (i < end) v[p][u] = ld_peer(reinterpret_cast<const char*>(a.in[p]) + i * 16);
+                if (i < end && TCCL_VIN(c, a, i)) v[p][u] = ld_peer(reinterpret_cast<const char*>(a.in[p]) + i * 16);
               }
             }
 #pragma unroll
@@ -131,7 +131,7 @@ struct AllReduceTwoShotPipe {
 #pragma unroll 4
         for (int k = j; k < SV; k += NB) {
           const uint64_t i = base + k;
-          if (i < end) {
+          if (i < end && TCCL_VOUT(c, a, i)) {
             const Vec16 v = ld_shared_v4(st + (size_t)k * 16);
             if (kNvls) {
               multimem_st(reinterpret_cast<char*>(a.mc_out) + i * 16, v);

@@ -8,6 +8,14 @@ extern "C" {
 
 int tccl_version(void) { return 100; }
 
+int tccl_debug_checks(void) {
+#ifdef TCCL_DEBUG_CHECKS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
 const char* tccl_error_string(int code) {
   if (code >= 0) return cudaGetErrorString((cudaError_t)code);
   switch (-code) {

@@ -133,11 +133,11 @@ struct AllReduceOneShotP2P {
         if (p < world) {
 #pragma unroll
           for (int u = 0; u < U; ++u)
-            if (i0 + u * bs < nvec) v[p][u] = ld_peer(vptr<T>(a.in[p], i0 + u * bs));
+            if (i0 + u * bs < nvec && TCCL_VIN(c, a, i0 + u * bs)) v[p][u] = ld_peer(vptr<T>(a.in[p], i0 + u * bs));
         }
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < nvec) {
+        if (i0 + u * bs < nvec && TCCL_VOUT(c, a, i0 + u * bs)) {
           if (W == 1) {  // nothing to add: stream the bits through
             st_local_cs(vptr<T>(a.out, i0 + u * bs), v[0][u]);
             continue;
@@ -179,10 +179,10 @@ struct AllReduceOneShotNvls {
       Vec16 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < nvec) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i0 + u * bs));
+        if (i0 + u * bs < nvec && TCCL_VIN(c, a, i0 + u * bs)) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, i0 + u * bs));
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < nvec) st_local(vptr<T>(a.out, i0 + u * bs), v[u]);
+        if (i0 + u * bs < nvec && TCCL_VOUT(c, a, i0 + u * bs)) st_local(vptr<T>(a.out, i0 + u * bs), v[u]);
     }
     const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if (tid < a.numel - nvec * VPT) {
@@ -240,7 +240,7 @@ struct AllReduceOneShotPush {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const uint64_t i = i0 + u * bs;
-        if (i < nvec) {
+        if (i < nvec && TCCL_VIN(c, a, i) && TCCL_IN_BOUNDS(c, i * 16, 16, slot, TCCL_W_INDEX_OUT)) {
           const Vec16 v = ld_peer(src + i * 16);
           if (kNvls) {
             multimem_st(c.mc_stage + mine + i * 16, v);
@@ -265,7 +265,7 @@ struct AllReduceOneShotPush {
         }
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < nvec) {
+        if (i0 + u * bs < nvec && TCCL_VOUT(c, a, i0 + u * bs)) {
           Acc<T> acc;
           acc.zero();
 #pragma unroll
@@ -315,11 +315,11 @@ struct AllReduceTwoShotP2P {
         if (p < world) {
 #pragma unroll
           for (int u = 0; u < U; ++u)
-            if (i0 + u * bs < n) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i0 + u * bs));
+            if (i0 + u * bs < n && TCCL_VIN(c, a, lo + i0 + u * bs)) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i0 + u * bs));
         }
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < n) {
+        if (i0 + u * bs < n && TCCL_VOUT(c, a, lo + i0 + u * bs)) {
           Acc<T> acc;
           acc.zero();
 #pragma unroll
@@ -363,10 +363,10 @@ struct AllReduceTwoShotNvls {
       Vec16 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < n) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i0 + u * bs));
+        if (i0 + u * bs < n && TCCL_VIN(c, a, lo + i0 + u * bs)) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i0 + u * bs));
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < n) multimem_st(vptr<T>(a.mc_out, lo + i0 + u * bs), v[u]);
+        if (i0 + u * bs < n && TCCL_VOUT(c, a, lo + i0 + u * bs)) multimem_st(vptr<T>(a.mc_out, lo + i0 + u * bs), v[u]);
     }
     const uint64_t tid = (uint64_t)bid * blockDim.x + threadIdx.x;
     if (c.rank == 0 && tid < a.numel - nvec * VPT) {
@@ -415,10 +415,10 @@ struct AllGatherPullP2P {
         Vec16 v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          if (i0 + u * bs < nvec) v[u] = ld_peer(vptr<T>(src, i0 + u * bs));
+          if (i0 + u * bs < nvec && TCCL_VIN(c, a, i0 + u * bs)) v[u] = ld_peer(vptr<T>(src, i0 + u * bs));
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          if (i0 + u * bs < nvec) st_local(dst + (i0 + u * bs) * 16, v[u]);
+          if (i0 + u * bs < nvec && TCCL_VOUT(c, a, (uint64_t)p * nvec + i0 + u * bs)) st_local(dst + (i0 + u * bs) * 16, v[u]);
       }
     }
     sync.exit(c, a.flags, bid);
@@ -457,10 +457,11 @@ struct AllGatherPush {
       Vec16 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < nvec) v[u] = ld_peer(vptr<T>(src, i0 + u * bs));
+        if (i0 + u * bs < nvec && TCCL_VIN(c, a, i0 + u * bs)) v[u] = ld_peer(vptr<T>(src, i0 + u * bs));
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        if (i0 + u * bs < nvec) put(c, a, world, base + (i0 + u * bs) * 16, v[u]);
+        if (i0 + u * bs < nvec && TCCL_IN_BOUNDS(c, base + (i0 + u * bs) * 16, 16, a.out_bytes, TCCL_W_INDEX_OUT))
+          put(c, a, world, base + (i0 + u * bs) * 16, v[u]);
     }
     sync.exit(c, a.flags, bid);
   }
@@ -487,10 +488,10 @@ struct ReduceScatter {
         Vec16 v[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          if (i0 + u * bs < per) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i0 + u * bs));
+          if (i0 + u * bs < per && TCCL_VIN(c, a, lo + i0 + u * bs)) v[u] = MultimemOps<T>::ld_reduce(vptr<T>(a.mc_in, lo + i0 + u * bs));
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          if (i0 + u * bs < per) st_local(vptr<T>(a.out, i0 + u * bs), v[u]);
+          if (i0 + u * bs < per && TCCL_VOUT(c, a, i0 + u * bs)) st_local(vptr<T>(a.out, i0 + u * bs), v[u]);
       }
     } else {
       TCCL_FOR_SLABS(U, per, bid, nb, i0) {
@@ -500,11 +501,11 @@ struct ReduceScatter {
           if (p < world) {
 #pragma unroll
             for (int u = 0; u < U; ++u)
-              if (i0 + u * bs < per) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i0 + u * bs));
+              if (i0 + u * bs < per && TCCL_VIN(c, a, lo + i0 + u * bs)) v[p][u] = ld_peer(vptr<T>(a.in[p], lo + i0 + u * bs));
           }
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          if (i0 + u * bs < per) {
+          if (i0 + u * bs < per && TCCL_VOUT(c, a, i0 + u * bs)) {
             Acc<T> acc;
             acc.zero();
 #pragma unroll

@@ -201,6 +201,24 @@ static __device__ __noinline__ void record_failure(const tccl_comm& c, int code,
   atomicExch(st + TCCL_ST_ABORT, 1u);
 }
 
+// Bounds checks of the TCCL_DEBUG_CHECKS build: `bytes` at offset `off` of a buffer whose usable
+// extent the host has passed along.  A miss records TCCL_BAD_INDEX with the offending offset and
+// the extent (low 32 bits each) and the caller SKIPS the access; nothing traps.  In the regular
+// build the macro is the constant true and the extents are not looked at.
+#ifdef TCCL_DEBUG_CHECKS
+static __device__ __noinline__ bool bad_index(const tccl_comm& c, uint64_t off, uint64_t extent, int where) {
+  record_failure(c, TCCL_BAD_INDEX, c.rank, where, (uint32_t)off, (uint32_t)extent);
+  return false;
+}
+#define TCCL_IN_BOUNDS(c, off, bytes, extent, where) \
+  (((uint64_t)(off) + (uint64_t)(bytes) <= (uint64_t)(extent)) ? true : bad_index((c), (uint64_t)(off), (uint64_t)(extent), (where)))
+#else
+#define TCCL_IN_BOUNDS(c, off, bytes, extent, where) true
+#endif
+// vector `vec` (16 bytes) of an input / output of the flat collectives
+#define TCCL_VIN(c, a, vec) TCCL_IN_BOUNDS(c, (uint64_t)(vec) * 16, 16, (a).in_bytes, TCCL_W_INDEX_IN)
+#define TCCL_VOUT(c, a, vec) TCCL_IN_BOUNDS(c, (uint64_t)(vec) * 16, 16, (a).out_bytes, TCCL_W_INDEX_OUT)
+
 __device__ __forceinline__ bool aborted(const tccl_comm& c) {
   return *reinterpret_cast<volatile uint32_t*>(status_of(c) + TCCL_ST_ABORT) != 0u;
 }

@@ -1,0 +1,203 @@
+// All-reduce with a quantised wire format: bf16 in, bf16 out, fp8 (e4m3) plus one
+// fp32 scale per 2048-element chunk on NVLink, fp32 accumulation at the owner.
+//
+// "Quantized communication" is the second thing the reference names as the
+// reason to write collectives as kernels at all (presentation.pdf, slide 4) and
+// does not build.  This is the two-shot all-reduce with both shots compressed:
+//   1. every rank cuts its input into chunks of 2048 elements, finds each chunk's
+//      absolute maximum, scales it to the e4m3 range, and stores the 2048 fp8
+//      bytes and the scale into slot [src] of the OWNER's staging area (chunks
+//      are dealt to the W owners slice by slice, as in reduce-scatter);
+//   2. (barrier) the owner dequantises the W copies of each of its chunks, sums
+//      them in fp32 in rank order, quantises the SUM the same way and stores it
+//      to every rank;
+//   3. (barrier) every rank dequantises all chunks into its bf16 output.
+// Per direction and GPU 2 (W-1)/W bytes per element cross the link (plus 0.2 %
+// of scales) against 2 (1 + 1/W) for the bf16 NVLS two-shot and 4 (W-1)/W for the
+// bf16 P2P two-shot.  The price is precision: each value is rounded to 3
+// mantissa bits twice (|error| <= 2^-4 of its chunk's maximum per rounding).
+//
+// CTA b works on the chunks whose index inside their slice is b, b + grid, ...
+// in all three steps, so the per-CTA barrier (same block index on all ranks) is
+// all the synchronisation the steps need.  The staging area is shared with the
+// fused GEMM kernels: the kernel opens with a barrier.  Every rank computes the
+// same bits: the sum is formed once, at the owner.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace tccl {
+
+constexpr int kQChunk = 2048;          // elements per chunk = per scale
+constexpr int kQThreads = kQChunk / 8; // 8 elements per thread
+
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+  uint16_t r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float2 e4m3x2_to_f32x2(uint16_t v) {
+  uint32_t h2;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(v));
+  return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
+// absolute maximum over the CTA (256 threads); every thread gets the result
+__device__ __forceinline__ float block_absmax(float v, float* s_red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();  // s_red may still be read from the previous chunk
+  if (lane == 0) s_red[warp] = v;
+  __syncthreads();
+  float m = s_red[0];
+#pragma unroll
+  for (int w = 1; w < kQThreads / 32; ++w) m = fmaxf(m, s_red[w]);
+  return m;
+}
+
+// 8 fp32 -> 8 fp8 bytes with the chunk's scale; returns the scale to store (value = byte * scale)
+__device__ __forceinline__ float quantise8(const float* f, float absmax, uint2& q) {
+  const float scale = fmaxf(absmax, 1e-30f) * (1.f / 448.f);  // 448 = largest finite e4m3
+  const float inv = 1.f / scale;
+  q.x = f32x2_to_e4m3x2(f[0] * inv, f[1] * inv) | (f32x2_to_e4m3x2(f[2] * inv, f[3] * inv) << 16);
+  q.y = f32x2_to_e4m3x2(f[4] * inv, f[5] * inv) | (f32x2_to_e4m3x2(f[6] * inv, f[7] * inv) << 16);
+  return scale;
+}
+__device__ __forceinline__ void dequantise8(const uint2& q, float scale, float* f) {
+  float2 a = e4m3x2_to_f32x2((uint16_t)(q.x & 0xffff)), b = e4m3x2_to_f32x2((uint16_t)(q.x >> 16));
+  float2 c = e4m3x2_to_f32x2((uint16_t)(q.y & 0xffff)), d = e4m3x2_to_f32x2((uint16_t)(q.y >> 16));
+  f[0] = a.x * scale; f[1] = a.y * scale; f[2] = b.x * scale; f[3] = b.y * scale;
+  f[4] = c.x * scale; f[5] = c.y * scale; f[6] = d.x * scale; f[7] = d.y * scale;
+}
+__device__ __forceinline__ void st_peer8(void* p, const uint2& v) {
+  asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ uint2 ld_peer8(const void* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.L1::no_allocate.v2.b32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float ld_peer_f32(const void* p) {
+  float v;
+  asm volatile("ld.relaxed.sys.global.L1::no_allocate.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+
+struct QuantAllReduce {
+  using Args = tccl_qar_args;
+  static constexpr int kMaxThreads = kQThreads, kMinBlocks = 2;
+
+  // staging layout of one rank (bytes): partials [src][cps][2048] | partial scales [src][cps] f32 |
+  //                                     sums [W * cps][2048]      | sum scales [W * cps] f32
+  static __host__ __device__ __forceinline__ uint64_t bytes_needed(uint64_t nchunks, int world) {
+    const uint64_t cps = (nchunks + world - 1) / world;
+    return 2ull * world * cps * (kQChunk + 16);  // scales padded: every section stays 16-byte aligned
+  }
+
+  static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
+    __shared__ float s_red[kQThreads / 32];
+    const uint64_t deadline = globaltimer() + c.timeout_ns;
+    const int W = c.world, me = c.rank, t = threadIdx.x;
+    const uint64_t nchunks = a.numel / kQChunk;
+    const uint64_t cps = (nchunks + W - 1) / W;  // chunks per slice (the last slices may be short or empty)
+    const uint64_t off_ps = (uint64_t)W * cps * kQChunk;
+    const uint64_t off_sum = off_ps + (((uint64_t)W * cps * 4 + 15) & ~15ull);
+    const uint64_t off_ss = off_sum + (uint64_t)W * cps * kQChunk;
+    const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(a.in);
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
+
+    barrier_p2p(c, bid, deadline);  // the staging area's previous user is done on every rank
+
+    // ---- 1: quantise the own input, chunk by chunk, into the owners' slots [me]
+    for (int k = 0; k < W; ++k) {
+      int q = me + 1 + k;  // start with the next rank: the W streams spread over the owners
+      if (q >= W) q -= W;
+      for (uint64_t j = bid; j < cps; j += nb) {
+        const uint64_t ch = (uint64_t)q * cps + j;
+        if (ch >= nchunks) break;
+        float f[8];
+        {
+          Acc<__nv_bfloat16> acc;
+          acc.zero();
+          acc.add(ld_peer(reinterpret_cast<const char*>(in) + (ch * kQChunk + (uint64_t)t * 8) * 2));
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = acc.a[e];
+        }
+        float m = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
+        m = block_absmax(m, s_red);
+        uint2 qv;
+        const float scale = quantise8(f, m, qv);
+        char* dst = c.stage[q];
+        st_peer8(dst + ((uint64_t)me * cps + j) * kQChunk + (uint64_t)t * 8, qv);
+        if (t == 0) st_relaxed_sys(reinterpret_cast<uint32_t*>(dst + off_ps) + (uint64_t)me * cps + j, __float_as_uint(scale));
+      }
+    }
+    barrier_p2p(c, bid, deadline);  // all partials of this CTA's chunks have landed at their owners
+
+    // ---- 2: sum the W copies of the own chunks in fp32, quantise the sum, store it to every rank
+    for (uint64_t j = bid; j < cps; j += nb) {
+      const uint64_t ch = (uint64_t)me * cps + j;
+      if (ch >= nchunks) break;
+      const char* mine = c.stage[me];
+      float s[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s[e] = 0.f;
+      for (int src = 0; src < W; ++src) {
+        const uint2 qv = ld_peer8(mine + ((uint64_t)src * cps + j) * kQChunk + (uint64_t)t * 8);
+        const float scale = ld_peer_f32(mine + off_ps + ((uint64_t)src * cps + j) * 4);
+        float f[8];
+        dequantise8(qv, scale, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[e] += f[e];
+      }
+      float m = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(s[e]));
+      m = block_absmax(m, s_red);
+      uint2 qv;
+      const float scale = quantise8(s, m, qv);
+      for (int p = 0; p < W; ++p) {
+        char* dst = c.stage[p];
+        st_peer8(dst + off_sum + ch * kQChunk + (uint64_t)t * 8, qv);
+        if (t == 0) st_relaxed_sys(reinterpret_cast<uint32_t*>(dst + off_ss) + ch, __float_as_uint(scale));
+      }
+    }
+    barrier_p2p(c, bid, deadline);  // all sums of this CTA's chunks have landed everywhere
+
+    // ---- 3: dequantise every slice's chunks of this CTA into the output
+    const char* mine = c.stage[me];
+    for (int q = 0; q < W; ++q) {
+      for (uint64_t j = bid; j < cps; j += nb) {
+        const uint64_t ch = (uint64_t)q * cps + j;
+        if (ch >= nchunks) break;
+        const uint2 qv = ld_peer8(mine + off_sum + ch * kQChunk + (uint64_t)t * 8);
+        const float scale = ld_peer_f32(mine + off_ss + ch * 4);
+        Acc<__nv_bfloat16> acc;
+        dequantise8(qv, scale, acc.a);
+        st_local(reinterpret_cast<char*>(out) + (ch * kQChunk + (uint64_t)t * 8) * 2, acc.pack());
+      }
+    }
+  }
+};
+
+}  // namespace tccl
+
+using namespace tccl;
+
+extern "C" uint64_t tccl_allreduce_fp8wire_stage_bytes(uint64_t numel, int world) {
+  return world >= 1 ? QuantAllReduce::bytes_needed(numel / kQChunk, world) : 0;
+}
+
+// bf16 only; numel % 2048 == 0; l->block == 256; needs tccl_allreduce_fp8wire_stage_bytes() of staging area
+extern "C" int tccl_allreduce_fp8wire(const tccl_comm* comm, const tccl_qar_args* args, const tccl_launch* l) {
+  if (l->block != kQThreads) return -TCCL_EINVAL;
+  if (l->n_emu == 0) {
+    if (!args->in || !args->out || args->numel == 0 || args->numel % kQChunk) return -TCCL_ESIZE;
+    if (((uintptr_t)args->in | (uintptr_t)args->out) & 15) return -TCCL_EALIGN;
+    if (QuantAllReduce::bytes_needed(args->numel / kQChunk, comm->world) > comm->stage_bytes) return -TCCL_ESIZE;
+  }
+  return launch_op<QuantAllReduce>(comm, args, l);
+}

@@ -70,7 +70,8 @@ enum tccl_error { TCCL_OK = 0, TCCL_TIMEOUT = 1, TCCL_BAD_INDEX = 2 };
 enum tccl_where {
   TCCL_W_BARRIER = 1, TCCL_W_MCBARRIER = 2, TCCL_W_CAS_SEND = 3, TCCL_W_CAS_WAIT = 4,
   TCCL_W_TREE_UP = 5, TCCL_W_TREE_DOWN = 6, TCCL_W_TILE = 7, TCCL_W_SIGNAL = 8,
-  TCCL_W_MBAR = 9
+  TCCL_W_MBAR = 9,
+  TCCL_W_INDEX_IN = 10, TCCL_W_INDEX_OUT = 11 /* TCCL_BAD_INDEX: an input / output offset beyond its extent */
 };
 
 /* launcher-side argument errors (returned negated) */
@@ -93,9 +94,12 @@ typedef struct tccl_comm {
   uint64_t tree_bytes;             /* bytes of the double-tree ring that follows the small-message region */
 } tccl_comm;
 
-/* double-tree ring: slot [tree][child slot][cta][chunk % depth], each TCCL_TREE_SLICE_BYTES long */
+/* double-tree ring.  First the small-message (flag-in-line) part: slots [tree][left, right, down][cta][seq % depth];
+ * then the chunked part: slots [tree][child slot][cta][chunk % depth].  Every slot is TCCL_TREE_SLICE_BYTES long. */
 #define TCCL_TREE_SLICE_BYTES 65536
 #define TCCL_TREE_RING_DEPTH 4
+#define TCCL_TREE_LL_MAX_CTAS 8
+#define TCCL_TREE_LL_BYTES (2 * 3 * TCCL_TREE_LL_MAX_CTAS * TCCL_TREE_RING_DEPTH * TCCL_TREE_SLICE_BYTES)
 
 /* Arguments shared by the data collectives. */
 typedef struct tccl_coll_args {
@@ -107,6 +111,9 @@ typedef struct tccl_coll_args {
   uint64_t numel;                 /* elements of the per-rank input */
   int32_t dtype;                  /* tccl_dtype */
   int32_t flags;                  /* TCCL_F_* */
+  uint64_t in_bytes;              /* bytes that may be read from every in[p] / mc_in ... */
+  uint64_t out_bytes;             /* ... and written at out / every out_peer[p] / mc_out: checked by the
+                                     TCCL_DEBUG_CHECKS build of the library, ignored by the regular one */
 } tccl_coll_args;
 
 #define TCCL_F_NO_EXIT_BARRIER 1 /* caller guarantees inputs stay untouched until peers are done */
@@ -127,6 +134,9 @@ typedef struct tccl_launch {
 } tccl_launch;
 
 int tccl_version(void);
+/* 1 if this library was built with TCCL_DEBUG_CHECKS (every vector offset of the flat collectives is
+ * checked against the extents in tccl_coll_args; a miss records TCCL_BAD_INDEX and skips the access) */
+int tccl_debug_checks(void);
 const char* tccl_error_string(int code);
 int tccl_num_sms(void);
 /* sizeof of an ABI struct by its name ("tccl_comm", ...), -1 if unknown */
@@ -188,6 +198,23 @@ typedef struct tccl_tree_args {
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
 /* CTAs per role that a ring of `tree_bytes` can serve (<= TCCL_TREE_MAX_CTAS) */
 int tccl_tree_max_ctas(uint64_t tree_bytes);
+/* Small messages: every 16-byte line on the wire carries 8 bytes of data and the call's sequence number
+ * twice, so a hop needs neither a release nor a counter.  numel * sizeof(T) <= 2 * ctas_per_role * 32 KiB,
+ * ctas_per_role <= TCCL_TREE_LL_MAX_CTAS.  Of args->buf only buf[rank] is used (this rank's own result
+ * buffer; may be null); nothing has to be in symmetric memory. */
+int tccl_allreduce_tree_ll(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
+
+/* ---- all-reduce with a quantised wire format ------------------------------- */
+typedef struct tccl_qar_args {
+  const void* in;   /* this rank's bf16 input, any device memory */
+  void* out;        /* this rank's bf16 output (may be `in`) */
+  uint64_t numel;   /* a multiple of 2048 */
+  int32_t flags;    /* reserved, 0 */
+} tccl_qar_args;
+/* bytes of staging area (per rank) the kernel needs */
+uint64_t tccl_allreduce_fp8wire_stage_bytes(uint64_t numel, int world);
+/* fp8 (e4m3) + one fp32 scale per 2048 elements on the wire, fp32 accumulation at the owner; l->block == 256 */
+int tccl_allreduce_fp8wire(const tccl_comm*, const tccl_qar_args*, const tccl_launch*);
 
 /* ---- fused all-reduce + bias + residual + RMSNorm ------------------------- */
 typedef struct tccl_arn_args {

@@ -43,7 +43,8 @@ constexpr int kTreeDepth = TCCL_TREE_RING_DEPTH;
 constexpr uint64_t kTreeSlice = TCCL_TREE_SLICE_BYTES;
 
 __host__ __device__ __forceinline__ int tree_max_ctas(uint64_t tree_bytes) {
-  const uint64_t k = tree_bytes / (4ull * kTreeDepth * kTreeSlice);
+  if (tree_bytes < TCCL_TREE_LL_BYTES) return 0;  // the small-message part comes first
+  const uint64_t k = (tree_bytes - TCCL_TREE_LL_BYTES) / (4ull * kTreeDepth * kTreeSlice);
   return (int)(k < TCCL_TREE_MAX_CTAS ? k : TCCL_TREE_MAX_CTAS);
 }
 
@@ -66,7 +67,7 @@ struct TreeAllReduce {
   static __device__ __forceinline__ char* ring(const tccl_comm& c, int rank, int tree, int cslot, int k, uint32_t seq) {
     const int kmax = tree_max_ctas(c.tree_bytes);
     const uint64_t idx = ((uint64_t)((tree * 2 + cslot) * kmax + k)) * kTreeDepth + (seq % kTreeDepth);
-    return c.stage[rank] + c.stage_bytes + c.ll_bytes + idx * kTreeSlice;
+    return c.stage[rank] + c.stage_bytes + c.ll_bytes + TCCL_TREE_LL_BYTES + idx * kTreeSlice;
   }
 
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {

@@ -122,9 +122,13 @@ def _base_args(world: WorldBase, x, dt: int, flags: int) -> L.CollArgs:
     for p, v in enumerate(world.peer_ptrs(x)):
         a.inp[p] = v
     a.mc_in = world.mc_ptr(x)
-    a.numel = world.local(x, world.local_ranks[0]).numel()
+    x0 = world.local(x, world.local_ranks[0])
+    a.numel = x0.numel()
     a.dtype = dt
     a.flags = flags
+    # extents for the bounds checks of the debug build (`debug_shrink_extent` is its test hook)
+    a.in_bytes = max(0, x0.numel() * x0.element_size() - world.config.debug_shrink_extent)
+    a.out_bytes = x0.numel() * x0.element_size()
     return a
 
 
@@ -212,6 +216,8 @@ def _plan_push(w, x, out, inplace, algo) -> Plan:
     for r in w.local_ranks:
         a = L.CollArgs()
         a.inp[r] = locs[r].data_ptr()  # the slots are found through the communicator itself
+        a.in_bytes = max(0, nbytes - w.config.debug_shrink_extent)
+        a.out_bytes = nbytes
         a.numel, a.dtype, a.flags = x0.numel(), dt, w.coll_flags()
         args[r] = a
     nvec = nbytes // 16
@@ -385,6 +391,7 @@ def _plan_all_gather(w, x, out, algo, sync_exit) -> Plan:
             algo = "pull"
     flags = w.coll_flags(sync_exit=sync_exit)
     base = _base_args(w, x, dt, flags)
+    base.out_bytes = nbytes * W
     vpt = 16 // x0.element_size()
     nvec = x0.numel() // vpt
     block = w.config.block
@@ -449,6 +456,7 @@ def _plan_reduce_scatter(w, x, out, algo, sync_exit) -> Plan:
         raise RuntimeError("nvls reduce-scatter needs NVLS multicast")
     flags = w.coll_flags(sync_exit=sync_exit)
     base = _base_args(w, x, dt, flags)
+    base.out_bytes = per * x0.element_size()
     args = {r: _copy_args(base) for r in w.local_ranks}
     block = w.config.block
     name = "tccl_reducescatter_nvls" if algo == "nvls" else "tccl_reducescatter_p2p"

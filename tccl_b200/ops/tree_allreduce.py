@@ -67,6 +67,8 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
     if nbytes % 16:
         raise ValueError("the element count must be a whole number of 16-byte vectors")
     W = w.world_size
+    if nbytes <= min(w.config.tree_ll_max_bytes, 2 * K["TCCL_TREE_LL_MAX_CTAS"] * (_SLICE // 2)):
+        return _plan_ll(w, x, out, inplace, x0, dt, nbytes)
     if inplace:
         work = x
     else:
@@ -101,6 +103,48 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
             a.out = o.data_ptr()
         args[r] = a
     go = w.prepare("tccl_allreduce_tree", args, 4 * k, w.config.block, dt)
+    if out is not None:
+        return Plan(w, go, args, result=_OUT)
+    if inplace:
+        return Plan(w, go, args, result=_X)
+    shape, dtype, dev = tuple(x0.shape), x0.dtype, x0.device
+    return Plan(w, go, args, alloc=lambda r: torch.empty(shape, dtype=dtype, device=dev))
+
+
+def _neighbours(a, W: int, r: int) -> None:
+    for t in (0, 1):
+        parent, left, right = tree_neighbours(W, r, t)
+        a.parent[t], a.left[t], a.right[t] = parent, left, right
+        a.child_slot[t] = 0
+        if parent >= 0:
+            a.child_slot[t] = 0 if tree_neighbours(W, parent, t)[1] == r else 1
+
+
+def _plan_ll(w: WorldBase, x, out, inplace: bool, x0, dt: int, nbytes: int) -> Plan:
+    """Small message: every line on the wire carries its own flag (``tree_allreduce_ll.cu``); the sums
+    come back through the ring too, so the result is written locally and nothing needs a scratch."""
+    W = w.world_size
+    k = max(1, min(K["TCCL_TREE_LL_MAX_CTAS"], -(-nbytes // 16384)))
+    while 2 * k * (_SLICE // 2) < nbytes:
+        k += 1
+    args = {}
+    for r in w.local_ranks:
+        a = L.TreeArgs()
+        xr = w.local(x, r)
+        a.inp = xr.data_ptr()
+        a.buf[r] = xr.data_ptr() if inplace else 0
+        a.numel = x0.numel()
+        a.chunk_vecs = 0
+        a.dtype = dt
+        a.ctas_per_role = k
+        _neighbours(a, W, r)
+        if out is not None:
+            o = w.local(out, r)
+            _check_out(o, xr)
+            a.out = o.data_ptr()
+        args[r] = a
+    block = 128 if nbytes <= 8192 else (256 if nbytes <= 65536 else 512)
+    go = w.prepare("tccl_allreduce_tree_ll", args, 4 * k, block, dt)
     if out is not None:
         return Plan(w, go, args, result=_OUT)
     if inplace:

@@ -73,11 +73,17 @@ class EmuWorld(WorldBase):
         # one allocation per rank: [staging area (its tail is the small-message region) | double-tree ring]
         self.stages = [torch.empty(self._stage_bytes + self.tree_bytes, dtype=torch.uint8, device=self.device)
                        for _ in range(W)]
+        self._zero_tree_ll()
         self.local_states = [torch.zeros(K["TCCL_LOCAL_WORDS"], dtype=torch.int32, device=self.device) for _ in range(W)]
         self.ll_bytes = min(2 << 20, self._stage_bytes // 4)
         self._keep = []
         self.plans = None  # emulated launches are not cached
         self._upload_comms()
+
+    def _zero_tree_ll(self):
+        """The small-message tree slots must not start out with bits that look like a flag."""
+        for s in self.stages:
+            s[self._stage_bytes: self._stage_bytes + K["TCCL_TREE_LL_BYTES"]].zero_()
 
     def _upload_comms(self):
         W = self.world_size
@@ -200,6 +206,7 @@ class EmuWorld(WorldBase):
         torch.cuda.synchronize(self.device)
         for t in self.flags + self.local_states:
             t.zero_()
+        self._zero_tree_ll()
         for k in ("_ag_seq", "_stage_user"):  # host-side mirrors of device state
             self.__dict__.pop(k, None)
         torch.cuda.synchronize(self.device)

@@ -67,9 +67,10 @@ class PlanCache(OrderedDict):
 
 
 def tree_ring_bytes(config: Config) -> int:
-    """Bytes of the double-tree ring: [tree][child slot][cta][depth] slices for ``tree_ctas`` CTAs per role."""
+    """Bytes of the double-tree ring: the small-message part, then [tree][child slot][cta][depth] slices
+    for ``tree_ctas`` CTAs per role."""
     k = max(1, min(int(config.tree_ctas), K["TCCL_TREE_MAX_CTAS"]))
-    return 4 * k * K["TCCL_TREE_RING_DEPTH"] * K["TCCL_TREE_SLICE_BYTES"]
+    return K["TCCL_TREE_LL_BYTES"] + 4 * k * K["TCCL_TREE_RING_DEPTH"] * K["TCCL_TREE_SLICE_BYTES"]
 
 
 class WorldBase:
@@ -183,6 +184,7 @@ class RealWorld(WorldBase):
         self.workspace = symm_mem.empty(self._flag_bytes + self._stage_bytes + self.tree_bytes, dtype=torch.uint8,
                                         device=self.device)
         self.workspace[: self._flag_bytes].zero_()
+        self._zero_tree_ll()
         self.local_state = torch.zeros(K["TCCL_LOCAL_WORDS"], dtype=torch.int32, device=self.device)
         ptrs, mc = self._resolve(self.workspace)
         self._nvls = bool(mc) and not self.config.disable_nvls
@@ -231,6 +233,12 @@ class RealWorld(WorldBase):
         hdl, base, mc, local_base = ent[:4]
         delta = t.data_ptr() - local_base
         return [b + delta for b in base], (mc + delta if mc else 0)
+
+    def _zero_tree_ll(self) -> None:
+        """The small-message tree slots are read before they are ever written (flags travel inside the
+        data): they must not start out with bits that look like a flag."""
+        lo = self._flag_bytes + self._stage_bytes
+        self.workspace[lo: lo + K["TCCL_TREE_LL_BYTES"]].zero_()
 
     def free(self, t: torch.Tensor) -> None:
         """Forget a symmetric allocation (and every cached launch that points into it)."""
@@ -317,6 +325,7 @@ class RealWorld(WorldBase):
         torch.cuda.synchronize(self.device)
         self._dist.barrier(self.group)
         self.workspace[: self._flag_bytes].zero_()
+        self._zero_tree_ll()
         self.local_state.zero_()
         for k in ("_ag_seq", "_stage_user"):  # host-side mirrors of device state
             self.__dict__.pop(k, None)

@@ -53,12 +53,19 @@ def headers():
     return sorted(list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")))
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    """Compile what is stale and link; returns the path of the shared library."""
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, debug_checks: bool = False) -> Path:
+    """Compile what is stale and link; returns the path of the shared library.
+
+    ``debug_checks=True`` builds the second flavour, ``libtccl_b200_dbg.so`` (``-DTCCL_DEBUG_CHECKS``):
+    the flat collectives check every vector offset against the extents the host passes along and,
+    on a miss, record ``TCCL_BAD_INDEX`` in the status words and skip the access.  The library is
+    loaded instead of the regular one when ``TCCL_DEBUG_CHECKS=1`` is set."""
     nvcc = _nvcc()
+    BUILD = PKG / ("_build_dbg" if debug_checks else "_build")
+    LIB = LIBDIR / ("libtccl_b200_dbg.so" if debug_checks else "libtccl_b200.so")
     BUILD.mkdir(exist_ok=True)
     LIBDIR.mkdir(exist_ok=True)
-    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
+    flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else []) + (["-DTCCL_DEBUG_CHECKS=1"] if debug_checks else [])
     hdr = headers()
     jobs = []
     objs = []
@@ -87,10 +94,12 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
                     if ptxas_info:
                         print(err, file=sys.stderr)
     if jobs or not LIB.exists():
-        cmd = [nvcc, "-shared", "-o", str(LIB), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
+        tmp = LIB.with_suffix(f".tmp{os.getpid()}.so")
+        cmd = [nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)  # atomic: nobody ever sees a half-written library
         if verbose:
             print(f"[tccl_b200.build] linked {LIB}", file=sys.stderr)
     return LIB
@@ -148,3 +157,4 @@ def build_host_tsan(verbose: bool = False) -> Path:
 if __name__ == "__main__":
     build_host(verbose=True, force="--force" in sys.argv)
     build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
+    build(verbose=True, force="--force" in sys.argv, debug_checks=True)

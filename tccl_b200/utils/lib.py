@@ -13,7 +13,10 @@ from pathlib import Path
 import torch
 
 PKG = Path(__file__).resolve().parent.parent
-LIB_PATH = PKG / "_lib" / "libtccl_b200.so"
+# TCCL_DEBUG_CHECKS=1 selects the library flavour whose flat-collective kernels check every vector
+# offset against the extents passed by the host (utils/build.py builds both)
+DEBUG_CHECKS = os.environ.get("TCCL_DEBUG_CHECKS", "") not in ("", "0")
+LIB_PATH = PKG / "_lib" / ("libtccl_b200_dbg.so" if DEBUG_CHECKS else "libtccl_b200.so")
 
 
 from .consts import K, MAX_WORLD  # noqa: E402,F401  (parsed from csrc/tccl_b200.h)
@@ -45,6 +48,8 @@ class CollArgs(C.Structure):
         ("numel", C.c_uint64),
         ("dtype", C.c_int32),
         ("flags", C.c_int32),
+        ("in_bytes", C.c_uint64),
+        ("out_bytes", C.c_uint64),
     ]
 
 
@@ -148,7 +153,7 @@ def lib() -> C.CDLL:
     if not LIB_PATH.exists() or os.environ.get("TCCL_REBUILD") == "1":
         from . import build as _build
 
-        _build.build()
+        _build.build(debug_checks=DEBUG_CHECKS)
     _lib = C.CDLL(str(LIB_PATH))
     _lib.tccl_error_string.restype = C.c_char_p
     _lib.tccl_error_string.argtypes = [C.c_int]

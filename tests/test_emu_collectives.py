@@ -280,13 +280,19 @@ def test_timeout_is_reported_not_hung(emu_worlds):
 
 @pytest.mark.parametrize("W", [1, 2, 3, 4, 5, 8])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("n,chunk_kb", [(8, 512), (4096, 1), (100000, 4), ((1 << 20) + 64, 64), (3 << 20, 512)])
-def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb):
+@pytest.mark.parametrize("n,chunk_kb,ll", [(8, 512, False), (8, 512, True), (4096, 1, False), (4096, 1, True),
+                                           (100000, 4, False), (65536 + 24, 4, True), ((1 << 20) + 64, 64, False),
+                                           (3 << 20, 512, False)])
+def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb, ll):
+    """`ll`: small messages take the kernel whose lines carry their own flags; with it switched off
+    the same sizes exercise the chunked kernel (ring, counters, acknowledgements) with tiny chunks."""
     import tccl_b200 as tccl
 
     w = emu_worlds(W)
     old = w.config.tree_chunk_bytes
+    old_ll = w.config.tree_ll_max_bytes
     w.config.tree_chunk_bytes = chunk_kb * 1024
+    w.config.tree_ll_max_bytes = old_ll if ll else 0
     try:
         x = make_inputs(w, W, n, dtype, 2000)
         keep = [p.clone() for p in x.parts]
@@ -316,6 +322,7 @@ def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb):
                 assert torch.equal(y[r], out[0])
     finally:
         w.config.tree_chunk_bytes = old
+        w.config.tree_ll_max_bytes = old_ll
 
 
 @pytest.mark.parametrize("W", [2, 4, 8])
