@@ -1,12 +1,15 @@
 """Per-tile timeline of the fused GEMM kernels on real GPUs: every CTA stamps
 %globaltimer when its producer may load a tile, when the tile's accumulator is
-complete and when its epilogue is done.  Prints, for rank 0, the kernel span
-and the distribution of epilogue durations and of the producer's wait per tile
-position — the numbers that say whether the kernel is MMA-, link- or
-arrival-bound.
+complete and when its epilogue is done (plus, in the CTA-pair kernels, when the
+epilogue warps are through with their data-mover phase and when the CTA leaves).
+Prints, for rank 0, the kernel span and the distribution of epilogue durations
+and of the producer's wait per tile position — the numbers that say whether the
+kernel is MMA-, link- or arrival-bound.  ncu cannot show this: it never wraps a
+multi-rank command.
 
-    python -m torch.distributed.run --nproc-per-node 8 bench/trace_fused.py
+    python -m torch.distributed.run --nproc-per-node 8 bench/trace_fused.py [--variant pair|single]
 """
+import argparse
 import os
 import sys
 
@@ -29,6 +32,13 @@ def summarize(name, tr, grid, comm_ctas=0):
     start = int(t[:, 63].min())
     us = lambda x: (x - start).double() / 1e3  # int64 arithmetic first: the timer is ~1e17 ns
     print(f"--- {name}: {t.shape[0]} GEMM CTAs; kernel start skew {float(us(t[:, 63]).max()):.1f} us")
+    if bool((t[:, 62] > 0).any()):
+        m = t[:, 62] > 0
+        print(f"  epilogue warps free (data-mover phase over) at: mean {float(us(t[:, 62][m]).mean()):.1f} max "
+              f"{float(us(t[:, 62][m]).max()):.1f} us")
+    if bool((t[:, 61] > 0).any()):
+        m = t[:, 61] > 0
+        print(f"  CTAs leave at: mean {float(us(t[:, 61][m]).mean()):.1f} max {float(us(t[:, 61][m]).max()):.1f} us")
     last = 0.0
     for i in range(8):
         load, ready, done = t[:, 4 * i], t[:, 4 * i + 1], t[:, 4 * i + 2]
@@ -44,6 +54,9 @@ def summarize(name, tr, grid, comm_ctas=0):
 
 
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--variant", default="pair", choices=["pair", "single"])
+    a = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     W = int(os.environ.get("WORLD_SIZE", 1))
@@ -54,13 +67,13 @@ def main():
     w = tccl.init()
     T, H, I = 4096, 4096, 14336
     Il, rows = I // W, T // W
-    grid = w.num_sms()
+    grid = w.num_sms() & ~1 if a.variant == "pair" else w.num_sms()
     tr = torch.zeros(grid * 64, dtype=torch.int64, device="cuda")
     a_r, wd_r = rnd((T, Il), 4000 + rank), rnd((H, Il), 5000 + rank, 0.02)
     for it in range(4):
         tr.zero_()
         dist.barrier()
-        tccl.gemm_reduce_scatter(a_r, wd_r, trace=tr)
+        tccl.gemm_reduce_scatter(a_r, wd_r, trace=tr, variant=a.variant)
         torch.cuda.synchronize()
     if rank == 0:
         summarize("gemm_reduce_scatter", tr, grid)
@@ -68,10 +81,10 @@ def main():
     for it in range(4):
         tr.zero_()
         dist.barrier()
-        tccl.all_gather_gemm(x_sh, wu_r, trace=tr)
+        tccl.all_gather_gemm(x_sh, wu_r, trace=tr, variant=a.variant)
         torch.cuda.synchronize()
     if rank == 0:
-        summarize("all_gather_gemm", tr, grid, comm_ctas=w.config.ag_movers)
+        summarize("all_gather_gemm", tr, grid, comm_ctas=0 if a.variant == "pair" else w.config.ag_movers)
     w.check()
     dist.barrier()
     dist.destroy_process_group()

@@ -39,6 +39,7 @@ struct alignas(64) AgGemmPairParams {
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank;
   int swiglu;
+  uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
 };
 
 struct AgGemmPairPolicy {
@@ -224,9 +225,10 @@ __device__ __forceinline__ void ag_gemm_pair_body(const tccl_comm& c, const AgGe
     tma_prefetch_desc(&p.map_a_full[parity]);
     tma_prefetch_desc(&p.map_b);
   }
-  run_mainloop2(p.shp, pol, &c, c.timeout_ns);
+  run_mainloop2(p.shp, pol, &c, c.timeout_ns, p.trace ? p.trace + (size_t)bid * 64 : nullptr);
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (p.trace) p.trace[(size_t)bid * 64 + 61] = globaltimer();
     __threadfence();
     const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_SCHED, 1u);
     if (done == (uint32_t)nb - 1u) {
@@ -275,6 +277,7 @@ static int fill_params(AgGemmPairParams* p, const tccl_ag_gemm_args* g, int worl
   p->tiles_n = (g->n + BN2 - 1) / BN2;
   p->tiles_m_per_rank = rows / 128;
   p->swiglu = g->swiglu;
+  p->trace = reinterpret_cast<uint64_t*>(g->trace);
   if (g->swiglu && (g->n % BN2)) return -TCCL_ESIZE;  // whole gate|up tiles only
   if (p->tiles_m_per_rank > TCCL_MAX_ROW_TILES) return -TCCL_ESIZE;
   return 0;

@@ -46,6 +46,7 @@ struct alignas(64) GemmRsPairParams {
   int tiles_m_per_rank;  // 128-row tiles per owner (even)
   int sync_entry;
   uint64_t half_bytes;   // bytes of one half of the staging area
+  uint64_t* trace;       // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
 };
 
 __device__ __forceinline__ void epi_bar2() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -218,7 +219,7 @@ __device__ __forceinline__ void gemm_rs_pair_body(const tccl_comm& c, const Gemm
     tma_prefetch_desc(&p.map_a);
     tma_prefetch_desc(&p.map_b);
   }
-  run_mainloop2(p.shp, pol, &c, c.timeout_ns);
+  run_mainloop2(p.shp, pol, &c, c.timeout_ns, p.trace ? p.trace + (size_t)bid * 64 : nullptr);
   // what is left of the reduction, all threads of the CTA, now waiting for flags
   {
     const int total = pol.tpo * 4;
@@ -240,6 +241,7 @@ __device__ __forceinline__ void gemm_rs_pair_body(const tccl_comm& c, const Gemm
   // the last CTA of this rank to finish publishes the new epoch and flips the staging half
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (p.trace) p.trace[(size_t)bid * 64 + 61] = globaltimer();
     __threadfence();
     const uint32_t done = atomicAdd(c.local + TCCL_LOCAL_SCHED, 1u);
     if (done == (uint32_t)nb - 1u) {
@@ -275,6 +277,7 @@ static int fill_params(GemmRsPairParams* p, const tccl_gemm_rs_args* g, int worl
   p->tiles_n = g->n / BN2;
   p->tiles_m_per_rank = g->m / world / 128;
   p->sync_entry = sync_entry;
+  p->trace = reinterpret_cast<uint64_t*>(g->trace);
   p->half_bytes = (stage_bytes / 2) & ~(uint64_t)1023;
   if (p->tiles_n * p->tiles_m_per_rank > TCCL_MAX_TILES) return -TCCL_ESIZE;
   if ((uint64_t)world * p->tiles_n * p->tiles_m_per_rank * kSlotBytes2 > p->half_bytes) return -TCCL_ESIZE;

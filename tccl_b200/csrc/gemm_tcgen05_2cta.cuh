@@ -124,8 +124,12 @@ struct Smem2 {
 //   epilogue_begin(quad, lane, ab)         -> epilogue warps, once, before they wait for the first accumulator
 //   between_tiles(quad, lane, ab)          -> epilogue warps, after a tile's accumulator has been released
 //   epilogue_finish(quad, lane, ab)
+// `trace` (optional, this CTA's 64 words of %globaltimer stamps): [63] kernel start, [62] side work of
+// epilogue_begin done, and for the CTA's i-th tile, i < 15: [4i] producer may load, [4i+1] accumulator
+// ready, [4i+2] epilogue done.
 template <class Policy>
-__device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* comm, uint64_t timeout_ns) {
+__device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* comm, uint64_t timeout_ns,
+                              uint64_t* trace = nullptr) {
   extern __shared__ uint8_t smem_raw[];
   Smem2 sm(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,6 +138,7 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
   const int num_kb = (shp.K + BK2 - 1) / BK2;
 
   if (threadIdx.x == 0) {
+    if (trace) trace[63] = globaltimer();
     *sm.abort_flag = 0;
     for (int s = 0; s < kStages2; ++s) {
       mbar_init(sm.full + s, 1);   // the leader producer's arrive.expect_tx (bytes of both CTAs)
@@ -165,6 +170,7 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
       for (int i = 0; ok && pol.tile(i, mt, nt, half); ++i) {
         mt += (int)cta;
         ok = pol.before_load(mt, nt, ab);
+        if (trace && i < 15) trace[4 * i] = globaltimer();
         const CUtensorMap* map_a;
         int ya;
         pol.a_tile(mt, map_a, ya);
@@ -223,6 +229,7 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
     bool ok = true;
     int mt, nt, half;
     pol.epilogue_begin(quad, lane, ab);  // the first accumulator is a whole tile away: time for side work
+    if (trace && quad == 0 && lane == 0) trace[62] = globaltimer();
     for (int i = 0; ok && pol.tile(i, mt, nt, half); ++i) {
       mt += (int)cta;
       const int acc = i & 1;
@@ -230,7 +237,9 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN2;
+      if (trace && i < 15 && quad == 0 && lane == 0) trace[4 * i + 1] = globaltimer();
       ok = pol.epilogue(mt, nt, half == 2 ? 128 : 0, half ? 128 : 256, taddr, quad, lane, ab, sm);
+      if (trace && i < 15 && quad == 0 && lane == 0) trace[4 * i + 2] = globaltimer();
       tc_fence_before();
       mbar_arrive_cluster(leader_tempty0 + (uint32_t)acc * 8);  // the leader's tmem_empty[acc], from either CTA
       if (ok) pol.between_tiles(quad, lane, ab);                // the accumulator is released: time for side work

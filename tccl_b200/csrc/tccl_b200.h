@@ -53,7 +53,8 @@ extern "C" {
 #define TCCL_LOCAL_RS_SEQ (TCCL_LOCAL_TREE_SEQ + 4 * TCCL_TREE_MAX_CTAS) /* pair GEMM -> RS calls completed (staging half) */
 #define TCCL_LOCAL_RS_NEXT (TCCL_LOCAL_RS_SEQ + 1)               /* pair GEMM -> RS: next reduction unit to hand out */
 #define TCCL_LOCAL_AG_SEQ (TCCL_LOCAL_RS_NEXT + 1)               /* pair AG -> GEMM calls completed (gather buffer half) */
-#define TCCL_LOCAL_WORDS (TCCL_LOCAL_AG_SEQ + 1)
+#define TCCL_LOCAL_TREE_LL_SEQ (TCCL_LOCAL_AG_SEQ + 1)            /* [role][cta]: calls of the small-message tree kernel */
+#define TCCL_LOCAL_WORDS (TCCL_LOCAL_TREE_LL_SEQ + 4 * 8)
 
 enum tccl_status_word {
   TCCL_ST_CODE = 0,   /* 0 = ok, else tccl_error */

@@ -16,8 +16,8 @@
 // tree ring of its own, so that it only ever holds lines of this format), the
 // slots [tree][left | right | down][k][seq % depth]; a slot holds 4096 lines =
 // 32 KiB of payload.  One slot per pipeline and call (the host picks K so that
-// the message fits), numbered by the pipeline's running chunk count, which it
-// shares with the chunked kernel (TCCL_LOCAL_TREE_SEQ).  A slot is reused
+// the message fits), numbered by the pipeline's own count of calls of this
+// kernel (TCCL_LOCAL_TREE_LL_SEQ).  A slot is reused
 // TCCL_TREE_RING_DEPTH calls later; a rank can run at most one call ahead of a
 // neighbour (it needs the neighbour's contribution to finish), so the old
 // lines have long been consumed, and their flags differ from the new number.
@@ -99,8 +99,10 @@ struct TreeAllReduceLL {
     const uint64_t tlo = tree ? half0 : 0, tn = tree ? nlines - half0 : half0;
     const uint64_t per = (tn + K - 1) / K;
     const uint64_t lo = tlo + min(per * (uint64_t)k, tn), n = min(per, tn - min(per * (uint64_t)k, tn));
-    uint32_t* seq_word = c.local + TCCL_LOCAL_TREE_SEQ + role * TCCL_TREE_MAX_CTAS + k;
-    const uint32_t g = *seq_word;  // this pipeline's running chunk number; one chunk per call here
+    // this kernel's own call count per pipeline: the chunked kernel's counters also pace its
+    // acknowledgements and must advance with its chunks only
+    uint32_t* seq_word = c.local + TCCL_LOCAL_TREE_LL_SEQ + role * TCCL_TREE_LL_MAX_CTAS + k;
+    const uint32_t g = *seq_word;
     const uint32_t flag = g + 1u;
     const char* in = reinterpret_cast<const char*>(a.in);
     char* res = reinterpret_cast<char*>(a.buf[me]);  // this rank's own result buffer (may be null)

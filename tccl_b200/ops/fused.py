@@ -85,10 +85,10 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, variant: str = "auto", w
     stage_bytes = (w.config.stage_mb << 20) - w.ll_bytes
     if variant not in ("auto", "pair", "single"):
         raise ValueError("variant must be 'auto', 'pair' or 'single'")
-    pair_ok = M % (W * 256) == 0 and lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) <= stage_bytes and trace is None
+    pair_ok = M % (W * 256) == 0 and lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) <= stage_bytes
     if variant == "pair" and not pair_ok:
         raise ValueError(f"the pair kernel needs M % {W * 256} == 0 and "
-                         f"{lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) >> 20} MiB of staging area (and no trace)")
+                         f"{lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) >> 20} MiB of staging area")
     pair = pair_ok and variant != "single"
     need = lib.tccl_gemm_rs_pair_stage_bytes(M, N, W) if pair else lib.tccl_gemm_rs_stage_bytes(M, N, W)
     if need > stage_bytes:
@@ -168,9 +168,9 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
     n_out = N // 2 if swiglu else N
     if variant not in ("auto", "pair", "single"):
         raise ValueError("variant must be 'auto', 'pair' or 'single'")
-    pair_ok = rows % 256 == 0 and trace is None
+    pair_ok = rows % 256 == 0
     if variant == "pair" and not pair_ok:
-        raise ValueError("the pair kernel needs (M / W) % 256 == 0 (and no trace)")
+        raise ValueError("the pair kernel needs (M / W) % 256 == 0")
     pair = pair_ok and variant != "single"
     half_bytes = 0
     ret_full = a_full

@@ -57,8 +57,6 @@ def double_tree_all_reduce(tensor, out=None, *, inplace: bool = False, world: Op
 
 
 def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
-    if inplace:
-        check_sym_tensor(w, x, "double_tree_all_reduce input")
     x0 = w.local(x, w.local_ranks[0])
     if not x0.is_cuda or not x0.is_contiguous() or x0.data_ptr() % 16:
         raise ValueError("the input must be a contiguous, 16-byte aligned CUDA tensor")
@@ -67,9 +65,11 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
     if nbytes % 16:
         raise ValueError("the element count must be a whole number of 16-byte vectors")
     W = w.world_size
-    if nbytes <= min(w.config.tree_ll_max_bytes, 2 * K["TCCL_TREE_LL_MAX_CTAS"] * (_SLICE // 2)):
+    if nbytes <= min(w.config.tree_ll_max_bytes, 2 * _ll_max_ctas(w) * (_SLICE // 2)):
         return _plan_ll(w, x, out, inplace, x0, dt, nbytes)
     if inplace:
+        # parents store the sum into their children's result buffer: it must be peer-mapped
+        check_sym_tensor(w, x, "double_tree_all_reduce(inplace=True) input above the small-message limit")
         work = x
     else:
         # the result buffer that parents store into: one scratch per size and dtype; every
@@ -120,11 +120,17 @@ def _neighbours(a, W: int, r: int) -> None:
             a.child_slot[t] = 0 if tree_neighbours(W, parent, t)[1] == r else 1
 
 
+def _ll_max_ctas(w: WorldBase) -> int:
+    """CTAs per role the small-message kernel may use: its ring's, and (emulated ranks share one GPU)
+    what is resident at once."""
+    return max(1, min(K["TCCL_TREE_LL_MAX_CTAS"], w.max_ctas() // 4))
+
+
 def _plan_ll(w: WorldBase, x, out, inplace: bool, x0, dt: int, nbytes: int) -> Plan:
     """Small message: every line on the wire carries its own flag (``tree_allreduce_ll.cu``); the sums
     come back through the ring too, so the result is written locally and nothing needs a scratch."""
     W = w.world_size
-    k = max(1, min(K["TCCL_TREE_LL_MAX_CTAS"], -(-nbytes // 16384)))
+    k = max(1, min(_ll_max_ctas(w), -(-nbytes // 16384)))
     while 2 * k * (_SLICE // 2) < nbytes:
         k += 1
     args = {}

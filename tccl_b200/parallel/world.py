@@ -224,6 +224,9 @@ class RealWorld(WorldBase):
         ent = self._handles.get(key)
         if ent is None:
             hdl = self._symm.rendezvous(t, self.group)
+            if hdl is None:
+                raise ValueError("this tensor does not live in symmetric memory: allocate it with "
+                                 "tccl_b200.empty() / world.empty() (or torch.distributed._symmetric_memory.empty)")
             base = [int(p) for p in hdl.buffer_ptrs]
             mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
             # the entry keeps `t` alive: a symmetric allocation stays mapped (and its

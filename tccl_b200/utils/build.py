@@ -154,7 +154,57 @@ def build_host_tsan(verbose: bool = False) -> Path:
     return exe
 
 
+def ptxas_table() -> str:
+    """Registers, spills and static shared memory of every kernel, as ptxas reports them
+    (``-Xptxas -v``), one markdown row per kernel template: the instance with the most registers."""
+    import re
+    import tempfile
+
+    nvcc = _nvcc()
+    rows = {}
+    with tempfile.TemporaryDirectory() as tmp:
+        for src in sources():
+            cmd = [nvcc, *NVCC_FLAGS, "-Xptxas", "-v", "-I", str(CSRC), "-c", str(src), "-o", os.path.join(tmp, src.stem + ".o")]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stderr}")
+            entry = None
+            spill = (0, 0, 0)
+            for line in r.stderr.splitlines():
+                m = re.search(r"Compiling entry function '(\S+)'", line)
+                if m:
+                    entry = m.group(1)
+                    continue
+                m = re.search(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads", line)
+                if m:
+                    spill = tuple(int(v) for v in m.groups())
+                    continue
+                m = re.search(r"Used (\d+) registers(?:, used (\d+) barriers)?(?:, (\d+) bytes cumulative stack size)?(?:, (\d+) bytes smem)?", line)
+                if m and entry:
+                    name = subprocess.run(["c++filt", entry], capture_output=True, text=True).stdout.strip() or entry
+                    name = re.sub(r"\(.*$", "", name)                       # drop the parameter list
+                    name = re.sub(r"^void ", "", name)
+                    fam = re.sub(r"(?<=<)(.*)(?=>)", lambda mm: re.sub(r"\b\d+\b", "*", mm.group(1)), name)
+                    fam = fam.replace("(__nv_bfloat16)", "").replace("tccl::", "")
+                    fam = re.sub(r"__nv_bfloat16|__half|float", "T", fam)
+                    regs, smem = int(m.group(1)), int(m.group(4) or 0)
+                    cur = rows.get((src.name, fam))
+                    if cur is None or regs > cur[0]:
+                        rows[(src.name, fam)] = (regs, spill, smem, (cur[3] if cur else 0) + 1)
+                    else:
+                        rows[(src.name, fam)] = (cur[0], cur[1], cur[2], cur[3] + 1)
+                    entry = None
+    out = ["| source | kernel (template arguments folded) | instances | max registers | stack / spill st / spill ld (B) | static smem (B) |",
+           "|---|---|---|---|---|---|"]
+    for (src, fam), (regs, spill, smem, cnt) in sorted(rows.items()):
+        out.append(f"| `{src}` | `{fam}` | {cnt} | {regs} | {spill[0]} / {spill[1]} / {spill[2]} | {smem} |")
+    return "\n".join(out)
+
+
 if __name__ == "__main__":
+    if "--ptxas-table" in sys.argv:
+        print(ptxas_table())
+        sys.exit(0)
     build_host(verbose=True, force="--force" in sys.argv)
     build(verbose=True, force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)
     build(verbose=True, force="--force" in sys.argv, debug_checks=True)

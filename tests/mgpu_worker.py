@@ -210,6 +210,45 @@ def main():
         return ok
     case("allreduce/tree", tree)
 
+    def tree_small():
+        """Small messages: the tree whose data lines carry their own flags; many calls in a row, sizes
+        changing, no synchronisation in between; in place and out of place."""
+        ok = True
+        outs = []
+        for it in range(40):
+            n = [8, 4096, 1 << 15, 1 << 16, 1000 * 8][it % 5]  # up to 256 KiB: nothing has to be symmetric
+            xs = [seeded(n, torch.float32, 7000 + 16 * it + r) for r in range(W)]
+            x = xs[rank].cuda()
+            if it % 2:
+                tccl.double_tree_all_reduce(x, inplace=True)
+                outs.append((x, torch.stack(xs).sum(0)))
+            else:
+                outs.append((tccl.double_tree_all_reduce(x), torch.stack(xs).sum(0)))
+        torch.cuda.synchronize()
+        for o, ref in outs:
+            ok = ok and bool(((o.cpu() - ref).abs() <= ref.abs() * 1e-5 + 1e-5).all())
+        return ok
+    case("allreduce/tree_small_messages", tree_small)
+
+    def quantized():
+        """fp8 on the wire: every rank gets the same bits, within two e4m3 roundings of the fp32 sum."""
+        ok = True
+        for n in (2048, 2048 * 37, 2048 * 4096):
+            xs = [seeded(n, torch.bfloat16, 8000 + r) for r in range(W)]
+            ref = torch.stack([x.float() for x in xs]).sum(0)
+            x = xs[rank].cuda()
+            for _ in range(2):
+                out = tccl.quantized_all_reduce(x)
+            torch.cuda.synchronize()
+            cmax = torch.stack([t.float().view(-1, 2048).abs().amax(1) for t in xs]).sum(0)
+            bound = ((cmax + ref.view(-1, 2048).abs().amax(1)) * 2 ** -4 * 1.05).unsqueeze(1).expand(-1, 2048).reshape(-1) + 1e-6
+            ok = ok and bool(((out.float().cpu() - ref).abs() <= bound).all())
+            gathered = [torch.empty_like(out) for _ in range(W)]
+            dist.all_gather(gathered, out)
+            ok = ok and all(torch.equal(g, out) for g in gathered)
+        return ok
+    case("allreduce/fp8_wire", quantized)
+
     def auto_paths():
         """`algo="auto"` end to end: push (small), one-shot (medium), staged two-shot (large, ordinary
         destination), in-place two-shot (large, symmetric)."""
