@@ -55,6 +55,8 @@ def nvlink_bytes_in(coll, algo, W, S):
     if coll == "allreduce":
         if algo in ("twoshot_nvls", "twoshot_pipe_nvls"):
             return S + S // W  # reduced slice in + every slice broadcast back (own included)
+        if algo == "fp8wire":
+            return (W - 1) * S // W  # one byte per element, there and back
         if algo.startswith("push"):
             return (W - 1) * S
         if algo == "oneshot_nvls":
@@ -258,6 +260,8 @@ def main():
                     if S >= (1 << 20):
                         algos += ["twoshot_pipe_nvls" if w.has_nvls and W > 2 else "twoshot_pipe_p2p"]
                     algos += ["tree"] if S >= 4096 else []
+                    if a.dtype == "bf16" and S % 4096 == 0 and (1 << 20) <= S <= (64 << 20):
+                        algos += ["fp8wire"]  # quantised wire format: not the same arithmetic, reported beside the rest
                 elif coll == "allgather":
                     algos = ["pull", "push"] + (["push_nvls"] if w.has_nvls else [])
                 else:
@@ -274,6 +278,10 @@ def main():
                         o = torch.empty_like(x)
                         fn = lambda: tccl.all_reduce(x, out=o, algo=algo)
                         res = lambda: o
+                    elif algo == "fp8wire":
+                        o = torch.empty_like(x)
+                        fn = lambda: tccl.quantized_all_reduce(x, out=o)
+                        res = lambda: o
                     elif algo == "tree":
                         fn = lambda: tccl.all_reduce(x, inplace=True, algo="tree")
                         res = lambda: x
@@ -284,7 +292,9 @@ def main():
                         res = lambda: y
                     fn()
                     torch.cuda.synchronize()
-                    worst = check_sum(res(), blk, n, partial_roundings=max(1, W.bit_length()) if algo == "tree" else 0)
+                    # fp8 wire: two roundings to 3 mantissa bits of values up to a chunk's maximum (<= ~5 sigma)
+                    pr = max(1, W.bit_length()) if algo == "tree" else (64 if algo == "fp8wire" else 0)
+                    worst = check_sum(res(), blk, n, partial_roundings=pr)
                 elif coll == "allgather":
                     if algo == "pull":
                         o = torch.empty(W * n, dtype=dtype, device=dev)

@@ -37,6 +37,7 @@ class Config:
     disable_nvls: bool = False        # never pick a multimem variant
     nvls_barrier: bool = False        # barrier flavour used inside data kernels
     force_variant: str = ""           # e.g. "oneshot_p2p"; empty = size-based choice
+    nvls_twoshot_min_bytes: int = 16 * 1024   # all-reduce with a switch and a symmetric destination: two-shot NVLS above this
     push_max_bytes: int = 64 * 1024       # all-reduce: push variant (one barrier, local sum) up to here
     oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
     staged_twoshot: bool = True           # large all-reduce into ordinary memory: two-shot via a cached symmetric buffer
@@ -44,6 +45,7 @@ class Config:
     tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
     tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
     tree_ll_max_bytes: int = 256 * 1024   # double-tree: up to here the flags travel inside the data lines
+    tree_bulk_min_bytes: int = 4 << 20    # double-tree: from here on the copy engine moves the data (cp.async.bulk)
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
     plan_cache_size: int = 512            # bound launches kept per communicator (least recently used go first)

@@ -17,9 +17,10 @@
 // bf16 P2P two-shot.  The price is precision: each value is rounded to 3
 // mantissa bits twice (|error| <= 2^-4 of its chunk's maximum per rounding).
 //
-// CTA b works on the chunks whose index inside their slice is b, b + grid, ...
-// in all three steps, so the per-CTA barrier (same block index on all ranks) is
-// all the synchronisation the steps need.  The staging area is shared with the
+// One warp handles one chunk at a time; warp w of CTA b works on the chunks whose
+// index inside their slice is 8 b + w, + 8 grid, ... in all three steps, so the
+// per-CTA barrier (same block index on all ranks) is all the synchronisation the
+// steps need.  The staging area is shared with the
 // fused GEMM kernels: the kernel opens with a barrier.  Every rank computes the
 // same bits: the sum is formed once, at the owner.
 #include <cuda_fp8.h>
@@ -42,27 +43,19 @@ __device__ __forceinline__ float2 e4m3x2_to_f32x2(uint16_t v) {
   return __half22float2(*reinterpret_cast<__half2*>(&h2));
 }
 
-// absolute maximum over the CTA (256 threads); every thread gets the result
-__device__ __forceinline__ float block_absmax(float v, float* s_red) {
+// absolute maximum over a warp; every lane gets the result
+__device__ __forceinline__ float warp_absmax(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  __syncthreads();  // s_red may still be read from the previous chunk
-  if (lane == 0) s_red[warp] = v;
-  __syncthreads();
-  float m = s_red[0];
-#pragma unroll
-  for (int w = 1; w < kQThreads / 32; ++w) m = fmaxf(m, s_red[w]);
-  return m;
+  return v;
 }
 
-// 8 fp32 -> 8 fp8 bytes with the chunk's scale; returns the scale to store (value = byte * scale)
-__device__ __forceinline__ float quantise8(const float* f, float absmax, uint2& q) {
-  const float scale = fmaxf(absmax, 1e-30f) * (1.f / 448.f);  // 448 = largest finite e4m3
-  const float inv = 1.f / scale;
+// the scale of a chunk whose absolute maximum is `absmax` (value = fp8 * scale; 448 = largest finite e4m3)
+__device__ __forceinline__ float chunk_scale(float absmax) { return fmaxf(absmax, 1e-30f) * (1.f / 448.f); }
+// 8 fp32 -> 8 fp8 bytes
+__device__ __forceinline__ void quantise8(const float* f, float inv, uint2& q) {
   q.x = f32x2_to_e4m3x2(f[0] * inv, f[1] * inv) | (f32x2_to_e4m3x2(f[2] * inv, f[3] * inv) << 16);
   q.y = f32x2_to_e4m3x2(f[4] * inv, f[5] * inv) | (f32x2_to_e4m3x2(f[6] * inv, f[7] * inv) << 16);
-  return scale;
 }
 __device__ __forceinline__ void dequantise8(const uint2& q, float scale, float* f) {
   float2 a = e4m3x2_to_f32x2((uint16_t)(q.x & 0xffff)), b = e4m3x2_to_f32x2((uint16_t)(q.x >> 16));
@@ -87,6 +80,7 @@ __device__ __forceinline__ float ld_peer_f32(const void* p) {
 struct QuantAllReduce {
   using Args = tccl_qar_args;
   static constexpr int kMaxThreads = kQThreads, kMinBlocks = 2;
+  static constexpr int kVec = kQChunk / 8 / 32;  // 16-byte input vectors per lane and chunk (8)
 
   // staging layout of one rank (bytes): partials [src][cps][2048] | partial scales [src][cps] f32 |
   //                                     sums [W * cps][2048]      | sum scales [W * cps] f32
@@ -95,17 +89,20 @@ struct QuantAllReduce {
     return 2ull * world * cps * (kQChunk + 16);  // scales padded: every section stays 16-byte aligned
   }
 
+  // One WARP per chunk: lane l owns the vectors l, l + 32, ... of the chunk, the maximum is a shuffle
+  // reduction, nothing goes through shared memory and no CTA-wide barrier sits between chunks.
   static __device__ void run(const tccl_comm& c, const Args& a, int bid, int nb) {
-    __shared__ float s_red[kQThreads / 32];
     const uint64_t deadline = globaltimer() + c.timeout_ns;
-    const int W = c.world, me = c.rank, t = threadIdx.x;
+    const int W = c.world, me = c.rank, lane = threadIdx.x & 31;
+    const uint64_t gw = (uint64_t)bid * (kQThreads / 32) + (threadIdx.x >> 5);  // this warp among the rank's warps
+    const uint64_t nw = (uint64_t)nb * (kQThreads / 32);
     const uint64_t nchunks = a.numel / kQChunk;
     const uint64_t cps = (nchunks + W - 1) / W;  // chunks per slice (the last slices may be short or empty)
     const uint64_t off_ps = (uint64_t)W * cps * kQChunk;
     const uint64_t off_sum = off_ps + (((uint64_t)W * cps * 4 + 15) & ~15ull);
     const uint64_t off_ss = off_sum + (uint64_t)W * cps * kQChunk;
-    const __nv_bfloat16* in = reinterpret_cast<const __nv_bfloat16*>(a.in);
-    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a.out);
+    const char* in = reinterpret_cast<const char*>(a.in);
+    char* out = reinterpret_cast<char*>(a.out);
 
     barrier_p2p(c, bid, deadline);  // the staging area's previous user is done on every rank
 
@@ -113,71 +110,95 @@ struct QuantAllReduce {
     for (int k = 0; k < W; ++k) {
       int q = me + 1 + k;  // start with the next rank: the W streams spread over the owners
       if (q >= W) q -= W;
-      for (uint64_t j = bid; j < cps; j += nb) {
+      for (uint64_t j = gw; j < cps; j += nw) {
         const uint64_t ch = (uint64_t)q * cps + j;
         if (ch >= nchunks) break;
-        float f[8];
-        {
-          Acc<__nv_bfloat16> acc;
-          acc.zero();
-          acc.add(ld_peer(reinterpret_cast<const char*>(in) + (ch * kQChunk + (uint64_t)t * 8) * 2));
+        Vec16 v[kVec];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) f[e] = acc.a[e];
-        }
+        for (int u = 0; u < kVec; ++u) v[u] = ld_peer(in + (ch * kQChunk + (uint64_t)(u * 32 + lane) * 8) * 2);
         float m = 0.f;
 #pragma unroll
-        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(f[e]));
-        m = block_absmax(m, s_red);
-        uint2 qv;
-        const float scale = quantise8(f, m, qv);
-        char* dst = c.stage[q];
-        st_peer8(dst + ((uint64_t)me * cps + j) * kQChunk + (uint64_t)t * 8, qv);
-        if (t == 0) st_relaxed_sys(reinterpret_cast<uint32_t*>(dst + off_ps) + (uint64_t)me * cps + j, __float_as_uint(scale));
+        for (int u = 0; u < kVec; ++u) {
+          Acc<__nv_bfloat16> acc;
+          acc.zero();
+          acc.add(v[u]);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(acc.a[e]));
+        }
+        const float scale = chunk_scale(warp_absmax(m)), inv = 1.f / scale;
+        char* dst = c.stage[q] + ((uint64_t)me * cps + j) * kQChunk;
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) {
+          Acc<__nv_bfloat16> acc;
+          acc.zero();
+          acc.add(v[u]);
+          uint2 qv;
+          quantise8(acc.a, inv, qv);
+          st_peer8(dst + (uint64_t)(u * 32 + lane) * 8, qv);
+        }
+        if (lane == 0)
+          st_relaxed_sys(reinterpret_cast<uint32_t*>(c.stage[q] + off_ps) + (uint64_t)me * cps + j, __float_as_uint(scale));
       }
     }
     barrier_p2p(c, bid, deadline);  // all partials of this CTA's chunks have landed at their owners
 
     // ---- 2: sum the W copies of the own chunks in fp32, quantise the sum, store it to every rank
-    for (uint64_t j = bid; j < cps; j += nb) {
+    const char* mine = c.stage[me];
+    for (uint64_t j = gw; j < cps; j += nw) {
       const uint64_t ch = (uint64_t)me * cps + j;
       if (ch >= nchunks) break;
-      const char* mine = c.stage[me];
-      float s[8];
+      float s[kVec][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s[e] = 0.f;
+      for (int u = 0; u < kVec; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[u][e] = 0.f;
       for (int src = 0; src < W; ++src) {
-        const uint2 qv = ld_peer8(mine + ((uint64_t)src * cps + j) * kQChunk + (uint64_t)t * 8);
+        const char* slot = mine + ((uint64_t)src * cps + j) * kQChunk;
         const float scale = ld_peer_f32(mine + off_ps + ((uint64_t)src * cps + j) * 4);
-        float f[8];
-        dequantise8(qv, scale, f);
+        uint2 qv[kVec];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) s[e] += f[e];
+        for (int u = 0; u < kVec; ++u) qv[u] = ld_peer8(slot + (uint64_t)(u * 32 + lane) * 8);
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) {
+          float f[8];
+          dequantise8(qv[u], scale, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[u][e] += f[e];
+        }
       }
       float m = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(s[e]));
-      m = block_absmax(m, s_red);
-      uint2 qv;
-      const float scale = quantise8(s, m, qv);
+      for (int u = 0; u < kVec; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, fabsf(s[u][e]));
+      const float scale = chunk_scale(warp_absmax(m)), inv = 1.f / scale;
+      uint2 qv[kVec];
+#pragma unroll
+      for (int u = 0; u < kVec; ++u) quantise8(s[u], inv, qv[u]);
       for (int p = 0; p < W; ++p) {
-        char* dst = c.stage[p];
-        st_peer8(dst + off_sum + ch * kQChunk + (uint64_t)t * 8, qv);
-        if (t == 0) st_relaxed_sys(reinterpret_cast<uint32_t*>(dst + off_ss) + ch, __float_as_uint(scale));
+        char* dst = c.stage[p] + off_sum + ch * kQChunk;
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) st_peer8(dst + (uint64_t)(u * 32 + lane) * 8, qv[u]);
+        if (lane == 0) st_relaxed_sys(reinterpret_cast<uint32_t*>(c.stage[p] + off_ss) + ch, __float_as_uint(scale));
       }
     }
     barrier_p2p(c, bid, deadline);  // all sums of this CTA's chunks have landed everywhere
 
-    // ---- 3: dequantise every slice's chunks of this CTA into the output
-    const char* mine = c.stage[me];
+    // ---- 3: dequantise every slice's chunks of this warp into the output
     for (int q = 0; q < W; ++q) {
-      for (uint64_t j = bid; j < cps; j += nb) {
+      for (uint64_t j = gw; j < cps; j += nw) {
         const uint64_t ch = (uint64_t)q * cps + j;
         if (ch >= nchunks) break;
-        const uint2 qv = ld_peer8(mine + off_sum + ch * kQChunk + (uint64_t)t * 8);
         const float scale = ld_peer_f32(mine + off_ss + ch * 4);
-        Acc<__nv_bfloat16> acc;
-        dequantise8(qv, scale, acc.a);
-        st_local(reinterpret_cast<char*>(out) + (ch * kQChunk + (uint64_t)t * 8) * 2, acc.pack());
+        uint2 qv[kVec];
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) qv[u] = ld_peer8(mine + off_sum + ch * kQChunk + (uint64_t)(u * 32 + lane) * 8);
+#pragma unroll
+        for (int u = 0; u < kVec; ++u) {
+          Acc<__nv_bfloat16> acc;
+          dequantise8(qv[u], scale, acc.a);
+          st_local(out + (ch * kQChunk + (uint64_t)(u * 32 + lane) * 8) * 2, acc.pack());
+        }
       }
     }
   }

@@ -196,6 +196,9 @@ typedef struct tccl_tree_args {
   int32_t right[2];
   int32_t child_slot[2];     /* 0 if this rank is its parent's left child, 1 if right */
 } tccl_tree_args;
+/* TCCL_TREE_BULK in l->meta: move the data with bulk async copies (shared memory -> peer) instead of
+ * 16-byte stores from the threads — the form for large messages */
+#define TCCL_TREE_BULK 256
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
 /* CTAs per role that a ring of `tree_bytes` can serve (<= TCCL_TREE_MAX_CTAS) */
 int tccl_tree_max_ctas(uint64_t tree_bytes);

@@ -33,9 +33,16 @@
 // its owner only; and a result buffer is written by the parent only after the
 // owner has contributed the same chunk of the same call.
 //
+// Two data paths.  Small slices: the threads store 16-byte vectors to the peer
+// themselves.  Large messages (`kBulk`): an SM sustains only a few GB/s of
+// posted remote stores, so the sums go to shared memory, 16 KiB at a time, and
+// the copy engine (cp.async.bulk, shared -> peer global) carries them; the down
+// workers do not touch the data at all — one thread bulk-loads a piece of the
+// own result buffer and bulk-stores it to both children.
+//
 // The element count must be a whole number of 16-byte vectors (the reference
 // asks the same: triton_double_tree_allreduce.py:346-348).
-#include "common.cuh"
+#include "gemm_tcgen05.cuh"  // bulk async copies, mbarriers
 
 namespace tccl {
 
@@ -48,11 +55,17 @@ __host__ __device__ __forceinline__ int tree_max_ctas(uint64_t tree_bytes) {
   return (int)(k < TCCL_TREE_MAX_CTAS ? k : TCCL_TREE_MAX_CTAS);
 }
 
-template <typename T>
+__device__ __forceinline__ void tree_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(gemm::smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(gemm::smem_u32(bar)) : "memory");
+}
+
+template <typename T, bool kBulk>
 struct TreeAllReduce {
   using Args = tccl_tree_args;
   static constexpr int kMaxThreads = 512, kMinBlocks = 1;
-  static constexpr int U = 4;  // vectors in flight per thread and source
+  static constexpr int U = 4;          // vectors in flight per thread and source
+  static constexpr int kSub = 1024;    // vectors per shared-memory piece of the bulk path (16 KiB)
 
   static __device__ __forceinline__ uint32_t* up_flag(const tccl_comm& c, int rank, int tree, int k, int slot) {
     return c.flags[rank] + TCCL_FLAG_TREE_UP + ((tree * TCCL_TREE_MAX_CTAS + k) * 2 + slot);
@@ -93,6 +106,20 @@ struct TreeAllReduce {
     const uint32_t base = *seq_word;  // chunks this pipeline has moved in earlier calls
     const int cslot = a.child_slot[tree];
 
+    __shared__ __align__(128) uint8_t s_buf[kBulk ? 2 : 1][kBulk ? kSub * 16 : 16];
+    __shared__ uint64_t s_bar[2];
+    __shared__ int s_abort;
+    uint32_t s_phase = 0;  // (thread 0) parity of the two load barriers
+    if (kBulk) {
+      if (t == 0) {
+        s_abort = 0;
+        gemm::mbar_init(s_bar + 0, 1);
+        gemm::mbar_init(s_bar + 1, 1);
+        gemm::fence_barrier_init();
+      }
+      __syncthreads();
+    }
+
     bool ok = true;
     if (is_up) {
       for (uint64_t n = 0; n < mine && ok; ++n) {
@@ -111,6 +138,48 @@ struct TreeAllReduce {
         const char* lring = left >= 0 ? ring(c, me, tree, 0, k, g) : nullptr;
         const char* rring = right >= 0 ? ring(c, me, tree, 1, k, g) : nullptr;
         char* pring = parent >= 0 ? ring(c, parent, tree, cslot, k, g) : nullptr;
+        if (kBulk) {
+          uint32_t sub = 0;
+          for (uint64_t s0 = lo; s0 < hi; s0 += kSub, ++sub) {
+            uint8_t* buf = s_buf[sub & 1];
+            const uint32_t cnt = (uint32_t)min((uint64_t)kSub, hi - s0);
+            if (sub >= 2) {
+              if (t == 0) gemm::bulk_wait_read<1>();  // the copies of two pieces ago have read this buffer
+              __syncthreads();
+            }
+            for (uint32_t j = t; j < cnt; j += nt) {
+              const uint64_t i = s0 + j;
+              Vec16 r = ld_peer(in + i * 16);
+              if (lring) {
+                Acc<T> acc;
+                acc.zero();
+                acc.add(r);
+                acc.add(ld_peer(lring + (i - lo) * 16));
+                if (rring) acc.add(ld_peer(rring + (i - lo) * 16));
+                r = acc.pack();
+              }
+              gemm::st_shared_v4(buf + (size_t)j * 16, r);
+            }
+            gemm::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk copies
+            __syncthreads();
+            if (t == 0) {
+              const uint32_t bytes = cnt * 16;
+              if (pring) {
+                gemm::bulk_store(pring + (s0 - lo) * 16, buf, bytes);
+              } else {  // the root: the final value goes to its own and its children's result buffers
+                gemm::bulk_store(res + s0 * 16, buf, bytes);
+                if (lres) gemm::bulk_store(lres + s0 * 16, buf, bytes);
+                if (rres) gemm::bulk_store(rres + s0 * 16, buf, bytes);
+                if (out) gemm::bulk_store(out + s0 * 16, buf, bytes);
+              }
+              gemm::bulk_commit();
+            }
+          }
+          if (t == 0) {
+            gemm::bulk_wait<0>();  // complete, not just read out of shared memory, before the flags go up
+            gemm::fence_proxy_async();
+          }
+        } else
         for (uint64_t i0 = lo + t; i0 < hi; i0 += (uint64_t)U * nt) {
           Vec16 vo[U], vl[U], vr[U];
 #pragma unroll
@@ -169,6 +238,39 @@ struct TreeAllReduce {
           const uint64_t clo = (2 * n + tree) * cv, chi = min(clo + cv, nvec);
           const uint64_t per = (chi - clo + K - 1) / K, lo = min(clo + per * k, chi), hi = min(lo + per, chi);
           constexpr int UD = 8;
+          if (kBulk) {
+            if (t == 0) {
+              gemm::fence_proxy_async();  // the parent's data, seen through the acquire above, is read by bulk copies next
+              const uint32_t nsub = (uint32_t)((hi - lo + kSub - 1) / kSub);
+              auto issue = [&](uint32_t sb) {
+                const uint64_t s0 = lo + (uint64_t)sb * kSub;
+                const uint32_t bytes = (uint32_t)min((uint64_t)kSub, hi - s0) * 16;
+                gemm::mbar_arrive_expect_tx(s_bar + (sb & 1), bytes);
+                tree_bulk_load(s_buf[sb & 1], res + s0 * 16, bytes, s_bar + (sb & 1));
+              };
+              gemm::Abort ab{&s_abort, &c, c.local + TCCL_LOCAL_STATUS, deadline};
+              if (nsub) issue(0);
+              for (uint32_t sb = 0; sb < nsub && ok; ++sb) {
+                if (sb + 1 < nsub) {
+                  gemm::bulk_wait_read<0>();  // the stores that last used the other buffer have read it
+                  issue(sb + 1);
+                }
+                ok = gemm::mbar_wait(s_bar + (sb & 1), (s_phase >> (sb & 1)) & 1u, ab);
+                if (!ok) break;
+                s_phase ^= 1u << (sb & 1);
+                const uint64_t s0 = lo + (uint64_t)sb * kSub;
+                const uint32_t bytes = (uint32_t)min((uint64_t)kSub, hi - s0) * 16;
+                if (lres) gemm::bulk_store(lres + s0 * 16, s_buf[sb & 1], bytes);
+                if (rres) gemm::bulk_store(rres + s0 * 16, s_buf[sb & 1], bytes);
+                if (out) gemm::bulk_store(out + s0 * 16, s_buf[sb & 1], bytes);
+                gemm::bulk_commit();
+              }
+              gemm::bulk_wait<0>();
+              gemm::fence_proxy_async();
+            }
+            ok = __syncthreads_and(ok);
+            if (!ok) break;
+          } else
           for (uint64_t i0 = lo + t; i0 < hi; i0 += (uint64_t)UD * nt) {
             Vec16 v[UD];
 #pragma unroll
@@ -211,10 +313,18 @@ extern "C" int tccl_allreduce_tree(const tccl_comm* comm, const tccl_tree_args* 
     if (K < 1 || K > tree_max_ctas(comm->tree_bytes) || l->grid != 4 * K) return -TCCL_ESIZE;
     if (args->chunk_vecs < 1 || args->chunk_vecs > (uint64_t)K * (TCCL_TREE_SLICE_BYTES / 16)) return -TCCL_ESIZE;
   }
+  if (l->meta & TCCL_TREE_BULK) {  // large messages: the copy engine carries the data
+    switch (dtype) {
+      case TCCL_BF16: return launch_op<TreeAllReduce<__nv_bfloat16, true>>(comm, args, l);
+      case TCCL_F32: return launch_op<TreeAllReduce<float, true>>(comm, args, l);
+      case TCCL_F16: return launch_op<TreeAllReduce<__half, true>>(comm, args, l);
+      default: return -TCCL_EDTYPE;
+    }
+  }
   switch (dtype) {
-    case TCCL_BF16: return launch_op<TreeAllReduce<__nv_bfloat16>>(comm, args, l);
-    case TCCL_F32: return launch_op<TreeAllReduce<float>>(comm, args, l);
-    case TCCL_F16: return launch_op<TreeAllReduce<__half>>(comm, args, l);
+    case TCCL_BF16: return launch_op<TreeAllReduce<__nv_bfloat16, false>>(comm, args, l);
+    case TCCL_F32: return launch_op<TreeAllReduce<float, false>>(comm, args, l);
+    case TCCL_F16: return launch_op<TreeAllReduce<__half, false>>(comm, args, l);
     default: return -TCCL_EDTYPE;
   }
 }

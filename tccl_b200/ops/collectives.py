@@ -167,11 +167,16 @@ def choose_all_reduce_algo(world: WorldBase, nbytes: int, symmetric_dst: bool) -
     nvls = world.has_nvls
     if world.world_size == 1:
         return "oneshot_p2p"
+    use_nvls = nvls and world.world_size > 2
+    if use_nvls and symmetric_dst and nbytes > cfg.nvls_twoshot_min_bytes:
+        # measured on 8 x B200: 18.8 us flat from 32 KiB to 512 KiB, against 19-21 us (push) and 21-31 us (one-shot)
+        if cfg.pipe_min_bytes and nbytes >= cfg.pipe_min_bytes:
+            return "twoshot_pipe_nvls"
+        return "twoshot_nvls"
     if nbytes <= cfg.push_max_bytes and nbytes % 16 == 0 and nbytes <= world.push_max_bytes():
-        return "push_nvls" if nvls and world.world_size > 2 else "push_p2p"
+        return "push_nvls" if use_nvls else "push_p2p"
     if not symmetric_dst or nbytes <= cfg.oneshot_max_bytes:
         return "oneshot_nvls" if nvls and world.world_size > 2 and nbytes <= 4 * cfg.oneshot_max_bytes else "oneshot_p2p"
-    use_nvls = nvls and world.world_size > 2
     if cfg.pipe_min_bytes and nbytes >= cfg.pipe_min_bytes:
         return "twoshot_pipe_nvls" if use_nvls else "twoshot_pipe_p2p"
     return "twoshot_nvls" if use_nvls else "twoshot_p2p"
@@ -245,7 +250,8 @@ def _plan_all_reduce(w, x, out, inplace, algo, sync_exit) -> Plan:
     if algo == "auto":
         x00 = x if w.plans is not None else x[w.local_ranks[0]]
         nb0 = x00.numel() * x00.element_size()
-        cand = choose_all_reduce_algo(w, nb0, True)
+        x_sym = _is_symmetric(w, x)
+        cand = choose_all_reduce_algo(w, nb0, x_sym and (inplace or (out is not None and _is_symmetric(w, out))))
         if cand.startswith("push") and x00.is_contiguous() and x00.data_ptr() % 16 == 0:
             return _plan_push(w, x, out, inplace, cand)
     check_sym_tensor(w, x, "all_reduce input")

@@ -59,7 +59,7 @@ def quantized_all_reduce(x, out=None, *, world: Optional[WorldBase] = None):
         args[r] = QarArgs(xs[r].data_ptr(), o.data_ptr(), n, 0)
     _stage_handoff(w, "fp8wire")
     cps = -(-(n // QUANT_CHUNK) // W)
-    grid = max(1, min(cps, 2 * w.max_ctas()))
+    grid = max(1, min(-(-cps // 8), 2 * w.max_ctas()))  # a CTA's 8 warps take 8 chunks at a time
     w.launch("tccl_allreduce_fp8wire", args, grid, 256)
     if out is not None:
         return out

@@ -102,7 +102,8 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
             _check_out(o, w.local(x, r))
             a.out = o.data_ptr()
         args[r] = a
-    go = w.prepare("tccl_allreduce_tree", args, 4 * k, w.config.block, dt)
+    bulk = K["TCCL_TREE_BULK"] if nbytes >= w.config.tree_bulk_min_bytes else 0
+    go = w.prepare("tccl_allreduce_tree", args, 4 * k, w.config.block, dt | bulk)
     if out is not None:
         return Plan(w, go, args, result=_OUT)
     if inplace:

@@ -325,6 +325,34 @@ def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb, ll):
         w.config.tree_ll_max_bytes = old_ll
 
 
+@pytest.mark.parametrize("W", [1, 2, 3, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [4096 + 8, (1 << 20) + 64, 3 << 20])
+def test_double_tree_bulk_copy_path(emu_worlds, W, dtype, n):
+    """The large-message data path (sums staged in shared memory, moved by bulk async copies), forced
+    on for sizes that end pieces and slices at odd places; same bits as the store path."""
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    old = (w.config.tree_bulk_min_bytes, w.config.tree_ll_max_bytes)
+    try:
+        x = make_inputs(w, W, n, dtype, 2500)
+        keep = [p.clone() for p in x.parts]
+        w.config.tree_ll_max_bytes = 0
+        w.config.tree_bulk_min_bytes = 1 << 40
+        plain = tccl.double_tree_all_reduce(x, world=w)
+        w.config.tree_bulk_min_bytes = 0
+        bulk = tccl.double_tree_all_reduce(x, world=w)
+        y = w.from_parts([p.clone() for p in keep])
+        tccl.all_reduce(y, inplace=True, algo="tree", world=w)
+        torch.cuda.synchronize()
+        w.check()
+        for r in range(W):
+            assert torch.equal(bulk[r], plain[r]) and torch.equal(y[r], plain[r]) and torch.equal(x[r], keep[r])
+    finally:
+        w.config.tree_bulk_min_bytes, w.config.tree_ll_max_bytes = old
+
+
 @pytest.mark.parametrize("W", [2, 4, 8])
 def test_double_tree_back_to_back_calls_of_changing_size(emu_worlds, W):
     """No barrier separates two tree all-reduces: sizes, chunking and CTA counts change from call

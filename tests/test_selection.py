@@ -37,7 +37,9 @@ def test_all_reduce_choice_follows_size_and_world():
     w8 = StubWorld(8, True)
     assert choose_all_reduce_algo(w8, 4096, True) == "push_nvls"
     assert choose_all_reduce_algo(w8, 64 * 1024, False) == "push_nvls"
-    assert choose_all_reduce_algo(w8, 256 * 1024, True) == "oneshot_nvls"
+    assert choose_all_reduce_algo(w8, 64 * 1024, True) == "twoshot_nvls"      # a switch and a symmetric destination
+    assert choose_all_reduce_algo(w8, 256 * 1024, True) == "twoshot_nvls"
+    assert choose_all_reduce_algo(w8, 256 * 1024, False) == "oneshot_nvls"
     assert choose_all_reduce_algo(w8, 16 << 20, True) == "twoshot_nvls"
     assert choose_all_reduce_algo(w8, 16 << 20, False).startswith("oneshot")  # no symmetric destination
     assert choose_all_reduce_algo(w8, 4100, True) == "oneshot_nvls"           # not a multiple of 16 bytes: no push
