@@ -43,9 +43,9 @@ class Config:
     staged_twoshot: bool = True           # large all-reduce into ordinary memory: two-shot via a cached symmetric buffer
     staged_max_bytes: int = 1 << 30       # ... up to this message size (the buffer is kept per size and dtype)
     tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
-    tree_ctas: int = 32                   # double-tree: CTAs per (tree, direction)
-    tree_ll_max_bytes: int = 256 * 1024   # double-tree: up to here the flags travel inside the data lines
-    tree_bulk_min_bytes: int = 4 << 20    # double-tree: from here on the copy engine moves the data (cp.async.bulk)
+    tree_ctas: int = 36                   # double-tree: CTAs per (tree, direction); 4 x 36 = 144 of 148 SMs
+    tree_ll_max_bytes: int = 2 << 20      # double-tree: up to here the flags travel inside the data lines
+    tree_pull_min_bytes: int = 0          # double-tree, chunked kernel: from here on children pull the sum from the parent
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
     plan_cache_size: int = 512            # bound launches kept per communicator (least recently used go first)

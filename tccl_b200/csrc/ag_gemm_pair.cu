@@ -39,6 +39,7 @@ struct alignas(64) AgGemmPairParams {
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank;
   int swiglu;
+  int movers_only;  // diagnostic (timeline tool): move the shard, compute nothing
   uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
 };
 
@@ -49,13 +50,14 @@ struct AgGemmPairPolicy {
   uint32_t epoch;
   int parity;
   int* s_last;  // shared: whether this CTA completed a batch of the data-mover phase
+  uint64_t* trace;  // this CTA's trace words, or null: [60 - 2 b] batch b stored, [59 - 2 b] batch b fenced
 
   __device__ __forceinline__ bool tile(int i, int& mt, int& nt, int& half) const {
     const int t = pair + i * npairs;
     const int tm2 = p->tiles_m_per_rank / 2, tn = p->tiles_n, W = c->world;
     const int own = tm2 * tn;
     half = 0;
-    if (t >= W * own) return false;
+    if (t >= W * own || p->movers_only) return false;
     if (t < own) {  // own rows first: no waiting
       mt = c->rank * p->tiles_m_per_rank + 2 * (t / tn);
       nt = t % tn;
@@ -121,7 +123,9 @@ struct AgGemmPairPolicy {
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // this CTA's share of the batch is stored
       if (t == 0) {
+        if (trace) trace[60 - 2 * b] = globaltimer();
         fence_acq_rel_sys();
+        if (trace) trace[59 - 2 * b] = globaltimer();
         const uint32_t done = atomicAdd(c->local + TCCL_LOCAL_AGCNT + b, 1u);
         *s_last = (done == (uint32_t)nb - 1u);
         if (*s_last) {
@@ -214,6 +218,7 @@ __device__ __forceinline__ void ag_gemm_pair_body(const tccl_comm& c, const AgGe
   __shared__ int s_last;
   AgGemmPairPolicy pol;
   pol.s_last = &s_last;
+  pol.trace = p.trace ? p.trace + (size_t)bid * 64 : nullptr;
   pol.c = &c;
   pol.p = &p;
   pol.pair = bid >> 1;
@@ -277,6 +282,7 @@ static int fill_params(AgGemmPairParams* p, const tccl_ag_gemm_args* g, int worl
   p->tiles_n = (g->n + BN2 - 1) / BN2;
   p->tiles_m_per_rank = rows / 128;
   p->swiglu = g->swiglu;
+  p->movers_only = g->lsu_movers == 2;
   p->trace = reinterpret_cast<uint64_t*>(g->trace);
   if (g->swiglu && (g->n % BN2)) return -TCCL_ESIZE;  // whole gate|up tiles only
   if (p->tiles_m_per_rank > TCCL_MAX_ROW_TILES) return -TCCL_ESIZE;

@@ -46,7 +46,9 @@ struct alignas(64) GemmRsPairParams {
   int tiles_m_per_rank;  // 128-row tiles per owner (even)
   int sync_entry;
   uint64_t half_bytes;   // bytes of one half of the staging area
-  uint64_t* trace;       // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
+  uint64_t* trace;       // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end,
+                         // [60] mainloop left, [59] first wait of the final reduction over, [58] / [57] units
+                         // reduced between tiles / in the final reduction
 };
 
 __device__ __forceinline__ void epi_bar2() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -61,6 +63,7 @@ struct GemmRsPairPolicy {
   int tpo2;   // pair tiles per owner
   uint32_t* pending_flag;  // epilogue issuer only
   int* s_unit;             // shared: the reduction unit the epilogue warps agreed on (-1 = none)
+  uint64_t* trace;         // this CTA's trace words, or null
 
   __device__ __forceinline__ char* stage_of(int rank) const { return c->stage[rank] + (uint64_t)parity * p->half_bytes; }
 
@@ -150,7 +153,10 @@ struct GemmRsPairPolicy {
       }
       epi_bar2();
       const int unit = *reinterpret_cast<volatile int*>(s_unit);
-      if (unit >= 0) reduce_unit(unit, quad * 32 + lane, 128);
+      if (unit >= 0) {
+        reduce_unit(unit, quad * 32 + lane, 128);
+        if (trace && quad == 0 && lane == 0) trace[58] += 1;
+      }
       epi_bar2();  // s_unit may be rewritten
       if (unit < 0) break;
     }
@@ -214,6 +220,7 @@ __device__ __forceinline__ void gemm_rs_pair_body(const tccl_comm& c, const Gemm
   pol.tpo2 = (p.tiles_m_per_rank / 2) * p.tiles_n;
   pol.pending_flag = nullptr;
   pol.s_unit = &s_unit;
+  pol.trace = p.trace ? p.trace + (size_t)bid * 64 : nullptr;
   if (p.sync_entry) barrier_p2p(c, bid, deadline);  // the staging area's previous user is done on every rank
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&p.map_a);
@@ -224,6 +231,7 @@ __device__ __forceinline__ void gemm_rs_pair_body(const tccl_comm& c, const Gemm
   {
     const int total = pol.tpo * 4;
     const int t = threadIdx.x;
+    if (pol.trace && t == 0) pol.trace[60] = globaltimer();
     for (;;) {
       if (t == 0) s_unit = (int)atomicAdd(c.local + TCCL_LOCAL_RS_NEXT, 1u);
       __syncthreads();
@@ -235,6 +243,10 @@ __device__ __forceinline__ void gemm_rs_pair_body(const tccl_comm& c, const Gemm
         ok = wait_reach(c.flags[c.rank] + TCCL_FLAG_TILE + t * TCCL_MAX_TILES + (u >> 2), pol.epoch, c, deadline, t,
                         TCCL_W_TILE);
       if (!__syncthreads_and(ok)) break;
+      if (pol.trace && t == 0) {
+        if (!pol.trace[59]) pol.trace[59] = globaltimer();
+        pol.trace[57] += 1;
+      }
       pol.reduce_unit(u, t, kThreads);
     }
   }

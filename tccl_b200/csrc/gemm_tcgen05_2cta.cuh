@@ -125,7 +125,7 @@ struct Smem2 {
 //   between_tiles(quad, lane, ab)          -> epilogue warps, after a tile's accumulator has been released
 //   epilogue_finish(quad, lane, ab)
 // `trace` (optional, this CTA's 64 words of %globaltimer stamps): [63] kernel start, [62] side work of
-// epilogue_begin done, and for the CTA's i-th tile, i < 15: [4i] producer may load, [4i+1] accumulator
+// epilogue_begin done, and for the CTA's i-th tile, i < 14 (words 56..61 belong to the policies): [4i] producer may load, [4i+1] accumulator
 // ready, [4i+2] epilogue done.
 template <class Policy>
 __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* comm, uint64_t timeout_ns,
@@ -170,7 +170,7 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
       for (int i = 0; ok && pol.tile(i, mt, nt, half); ++i) {
         mt += (int)cta;
         ok = pol.before_load(mt, nt, ab);
-        if (trace && i < 15) trace[4 * i] = globaltimer();
+        if (trace && i < 14) trace[4 * i] = globaltimer();
         const CUtensorMap* map_a;
         int ya;
         pol.a_tile(mt, map_a, ya);
@@ -237,9 +237,9 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN2;
-      if (trace && i < 15 && quad == 0 && lane == 0) trace[4 * i + 1] = globaltimer();
+      if (trace && i < 14 && quad == 0 && lane == 0) trace[4 * i + 1] = globaltimer();
       ok = pol.epilogue(mt, nt, half == 2 ? 128 : 0, half ? 128 : 256, taddr, quad, lane, ab, sm);
-      if (trace && i < 15 && quad == 0 && lane == 0) trace[4 * i + 2] = globaltimer();
+      if (trace && i < 14 && quad == 0 && lane == 0) trace[4 * i + 2] = globaltimer();
       tc_fence_before();
       mbar_arrive_cluster(leader_tempty0 + (uint32_t)acc * 8);  // the leader's tmem_empty[acc], from either CTA
       if (ok) pol.between_tiles(quad, lane, ab);                // the accumulator is released: time for side work

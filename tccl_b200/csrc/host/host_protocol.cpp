@@ -93,6 +93,9 @@ uint32_t* down_flag(const HostComm& c, int rank, int tree, int k) {
 uint32_t* ack_flag(const HostComm& c, int rank, int tree, int k) {
   return c.flags[rank] + TCCL_FLAG_TREE_ACK + (tree * TCCL_TREE_MAX_CTAS + k);
 }
+uint32_t* dack_flag(const HostComm& c, int rank, int tree, int k, int slot) {
+  return c.flags[rank] + TCCL_FLAG_TREE_DACK + ((tree * TCCL_TREE_MAX_CTAS + k) * 2 + slot);
+}
 
 struct TreeJob {
   const float* in;              // this rank's input (read by nobody else)
@@ -101,6 +104,7 @@ struct TreeJob {
   uint64_t numel, chunk;
   uint64_t ring_stride;         // elements per ring slot: fixed for the communicator, >= any chunk
   int parent[2], left[2], right[2], child_slot[2];
+  bool pull_down;               // way down: children copy the sum out of their parent's buffer and acknowledge
 };
 constexpr int kDepth = TCCL_TREE_RING_DEPTH;
 
@@ -137,8 +141,10 @@ void tree_worker(const HostComm& c, const TreeJob& j, int tree, bool is_up, clk:
           pr[i - lo] = v;
         } else {  // the root: the final value goes to its own and its children's result buffers
           j.buf[me][i] = v;
-          if (left >= 0) j.buf[left][i] = v;
-          if (right >= 0) j.buf[right][i] = v;
+          if (!j.pull_down) {
+            if (left >= 0) j.buf[left][i] = v;
+            if (right >= 0) j.buf[right][i] = v;
+          }
         }
       }
       if (parent >= 0) {
@@ -150,16 +156,27 @@ void tree_worker(const HostComm& c, const TreeJob& j, int tree, bool is_up, clk:
       if (left >= 0) A(ack_flag(c, left, tree, 0)).store(g + 1u, std::memory_order_release);
       if (right >= 0) A(ack_flag(c, right, tree, 0)).store(g + 1u, std::memory_order_release);
     }
-  } else if (parent >= 0) {
-    for (uint64_t n = 0; n < mine; ++n) {
+  } else {
+    for (uint64_t n = 0; parent >= 0 && n < mine; ++n) {
       if (f.stop_after_chunk >= 0 && n >= (uint64_t)f.stop_after_chunk) return;
       const uint32_t g = base + (uint32_t)n;
       if (!wait_reach(down_flag(c, me, tree, 0), g + 1u, c, deadline, 2 + tree, parent, TCCL_W_TREE_DOWN)) return;
       const uint64_t lo = (2 * n + tree) * j.chunk, hi = std::min(lo + j.chunk, j.numel);
-      if (left >= 0) std::memcpy(j.buf[left] + lo, j.buf[me] + lo, (hi - lo) * sizeof(float));
-      if (right >= 0) std::memcpy(j.buf[right] + lo, j.buf[me] + lo, (hi - lo) * sizeof(float));
+      if (j.pull_down) {
+        std::memcpy(j.buf[me] + lo, j.buf[parent] + lo, (hi - lo) * sizeof(float));
+        A(dack_flag(c, parent, tree, 0, cslot)).store(g + 1u, std::memory_order_release);
+      } else {
+        if (left >= 0) std::memcpy(j.buf[left] + lo, j.buf[me] + lo, (hi - lo) * sizeof(float));
+        if (right >= 0) std::memcpy(j.buf[right] + lo, j.buf[me] + lo, (hi - lo) * sizeof(float));
+      }
       if (left >= 0) A(down_flag(c, left, tree, 0)).store(g + 1u, std::memory_order_release);
       if (right >= 0) A(down_flag(c, right, tree, 0)).store(g + 1u, std::memory_order_release);
+    }
+    if (j.pull_down && mine) {
+      // the caller may overwrite this rank's buffer once the call returns: wait until the children have copied it
+      const uint32_t want = base + (uint32_t)mine;
+      if (left >= 0 && !wait_reach(dack_flag(c, me, tree, 0, 0), want, c, deadline, 2 + tree, left, TCCL_W_TREE_DOWN)) return;
+      if (right >= 0 && !wait_reach(dack_flag(c, me, tree, 0, 1), want, c, deadline, 2 + tree, right, TCCL_W_TREE_DOWN)) return;
     }
   }
   *seq_word = base + (uint32_t)mine;
@@ -184,6 +201,7 @@ struct hp_tree {
   uint64_t ring[TCCL_MAX_WORLD];  // 4 * TCCL_TREE_RING_DEPTH * ring_stride floats per rank
   uint64_t numel, chunk, ring_stride;
   int32_t parent[2], left[2], right[2], child_slot[2];
+  int32_t pull_down, pad_;        // 1: children copy the sum out of their parent's buffer (the large-message form)
 };
 
 static HostComm to_comm(const hp_comm* h) {
@@ -220,6 +238,7 @@ int hp_tree_allreduce(const hp_comm* h, const hp_tree* t, const hp_faults* f) {
   j.numel = t->numel;
   j.chunk = t->chunk;
   j.ring_stride = t->ring_stride;
+  j.pull_down = t->pull_down != 0;
   if (j.chunk > j.ring_stride) return 0;
   for (int i = 0; i < 2; ++i) {
     j.parent[i] = t->parent[i];
@@ -245,7 +264,7 @@ int hp_tree_allreduce(const hp_comm* h, const hp_tree* t, const hp_faults* f) {
 // GPU side cannot have.  Returns 0 on success, a positive code otherwise.
 extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds) {
   if (world < 1 || world > TCCL_MAX_WORLD) return 100;
-  constexpr int kCalls = 4;  // back to back, no barrier in between, alternating chunk sizes
+  constexpr int kCalls = 6;  // back to back, no barrier in between, alternating chunk sizes and forms of the way down
   std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
   std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
   std::vector<std::vector<float>> data(world, std::vector<float>(numel));
@@ -307,6 +326,7 @@ extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds) 
         t.numel = (uint64_t)numel;
         t.chunk = (uint64_t)((call & 1) ? std::max(1, chunk / 2) : chunk);
         t.ring_stride = (uint64_t)chunk;
+        t.pull_down = (call >> 1) & 1;  // push, push, pull, pull: both forms and the change between them
         for (int tr = 0; tr < 2; ++tr) {
           int parent, left, right;
           nbr(world, r, tr, &parent, &left, &right);

@@ -38,7 +38,8 @@ extern "C" {
 #define TCCL_FLAG_AG (TCCL_FLAG_LL + 1024)                            /* [src][row tile] AG->GEMM */
 #define TCCL_MAX_ROW_TILES 256
 #define TCCL_FLAG_TREE_ACK (TCCL_FLAG_AG + TCCL_MAX_WORLD * TCCL_MAX_ROW_TILES) /* [tree][cta]: my chunks the parent has consumed */
-#define TCCL_FLAG_WORDS (TCCL_FLAG_TREE_ACK + 2 * TCCL_TREE_MAX_CTAS)
+#define TCCL_FLAG_TREE_DACK (TCCL_FLAG_TREE_ACK + 2 * TCCL_TREE_MAX_CTAS) /* [tree][cta][2 slots]: slices a child has pulled */
+#define TCCL_FLAG_WORDS (TCCL_FLAG_TREE_DACK + 2 * TCCL_TREE_MAX_CTAS * 2)
 
 /* local (non peer-visible) state, in 32-bit words */
 #define TCCL_LOCAL_EPOCH 0                                       /* [block] p2p barrier   */
@@ -54,7 +55,7 @@ extern "C" {
 #define TCCL_LOCAL_RS_NEXT (TCCL_LOCAL_RS_SEQ + 1)               /* pair GEMM -> RS: next reduction unit to hand out */
 #define TCCL_LOCAL_AG_SEQ (TCCL_LOCAL_RS_NEXT + 1)               /* pair AG -> GEMM calls completed (gather buffer half) */
 #define TCCL_LOCAL_TREE_LL_SEQ (TCCL_LOCAL_AG_SEQ + 1)            /* [role][cta]: calls of the small-message tree kernel */
-#define TCCL_LOCAL_WORDS (TCCL_LOCAL_TREE_LL_SEQ + 4 * 8)
+#define TCCL_LOCAL_WORDS (TCCL_LOCAL_TREE_LL_SEQ + 4 * 32)
 
 enum tccl_status_word {
   TCCL_ST_CODE = 0,   /* 0 = ok, else tccl_error */
@@ -99,7 +100,7 @@ typedef struct tccl_comm {
  * then the chunked part: slots [tree][child slot][cta][chunk % depth].  Every slot is TCCL_TREE_SLICE_BYTES long. */
 #define TCCL_TREE_SLICE_BYTES 65536
 #define TCCL_TREE_RING_DEPTH 4
-#define TCCL_TREE_LL_MAX_CTAS 8
+#define TCCL_TREE_LL_MAX_CTAS 32
 #define TCCL_TREE_LL_BYTES (2 * 3 * TCCL_TREE_LL_MAX_CTAS * TCCL_TREE_RING_DEPTH * TCCL_TREE_SLICE_BYTES)
 
 /* Arguments shared by the data collectives. */
@@ -196,9 +197,10 @@ typedef struct tccl_tree_args {
   int32_t right[2];
   int32_t child_slot[2];     /* 0 if this rank is its parent's left child, 1 if right */
 } tccl_tree_args;
-/* TCCL_TREE_BULK in l->meta: move the data with bulk async copies (shared memory -> peer) instead of
- * 16-byte stores from the threads — the form for large messages */
-#define TCCL_TREE_BULK 256
+/* TCCL_TREE_PULL_DOWN in l->meta: on the way down the children load the sum from their parent's result
+ * buffer instead of the parent storing it into theirs — the form for large messages (buf must then be
+ * readable by the children until they have acknowledged, which the kernel waits for) */
+#define TCCL_TREE_PULL_DOWN 256
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
 /* CTAs per role that a ring of `tree_bytes` can serve (<= TCCL_TREE_MAX_CTAS) */
 int tccl_tree_max_ctas(uint64_t tree_bytes);

@@ -33,16 +33,21 @@
 // its owner only; and a result buffer is written by the parent only after the
 // owner has contributed the same chunk of the same call.
 //
-// Two data paths.  Small slices: the threads store 16-byte vectors to the peer
-// themselves.  Large messages (`kBulk`): an SM sustains only a few GB/s of
-// posted remote stores, so the sums go to shared memory, 16 KiB at a time, and
-// the copy engine (cp.async.bulk, shared -> peer global) carries them; the down
-// workers do not touch the data at all — one thread bulk-loads a piece of the
-// own result buffer and bulk-stores it to both children.
+// Two forms of the way down.  Push (`kPullDown` false): a parent stores the sum
+// into its children's result buffers, as described above: one crossing per
+// level, the form for latency.  Pull (`kPullDown` true): a parent only bumps its
+// children's DOWN counter and each child LOADS the slice from the parent's
+// result buffer.  An SM sustains only a few GB/s of peer traffic, and a pushing
+// parent has two children to serve with the same CTAs; pulling spreads the down
+// traffic over the children's SMs, which is what large messages need.  A parent
+// whose buffer is pulled from must not return while a child may still be
+// reading (its caller may overwrite the buffer next): each child acknowledges
+// every slice it has pulled (DACK counter at the parent) and the parent's down
+// worker waits for the last acknowledgement before it leaves.
 //
 // The element count must be a whole number of 16-byte vectors (the reference
 // asks the same: triton_double_tree_allreduce.py:346-348).
-#include "gemm_tcgen05.cuh"  // bulk async copies, mbarriers
+#include "common.cuh"
 
 namespace tccl {
 
@@ -55,17 +60,11 @@ __host__ __device__ __forceinline__ int tree_max_ctas(uint64_t tree_bytes) {
   return (int)(k < TCCL_TREE_MAX_CTAS ? k : TCCL_TREE_MAX_CTAS);
 }
 
-__device__ __forceinline__ void tree_bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(gemm::smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(gemm::smem_u32(bar)) : "memory");
-}
-
-template <typename T, bool kBulk>
+template <typename T, bool kPullDown>
 struct TreeAllReduce {
   using Args = tccl_tree_args;
   static constexpr int kMaxThreads = 512, kMinBlocks = 1;
-  static constexpr int U = 4;          // vectors in flight per thread and source
-  static constexpr int kSub = 1024;    // vectors per shared-memory piece of the bulk path (16 KiB)
+  static constexpr int U = 4;  // vectors in flight per thread and source
 
   static __device__ __forceinline__ uint32_t* up_flag(const tccl_comm& c, int rank, int tree, int k, int slot) {
     return c.flags[rank] + TCCL_FLAG_TREE_UP + ((tree * TCCL_TREE_MAX_CTAS + k) * 2 + slot);
@@ -75,6 +74,10 @@ struct TreeAllReduce {
   }
   static __device__ __forceinline__ uint32_t* ack_flag(const tccl_comm& c, int rank, int tree, int k) {
     return c.flags[rank] + TCCL_FLAG_TREE_ACK + (tree * TCCL_TREE_MAX_CTAS + k);
+  }
+  // at the parent, written by the child in `slot`: slices of the way down that the child has pulled
+  static __device__ __forceinline__ uint32_t* dack_flag(const tccl_comm& c, int rank, int tree, int k, int slot) {
+    return c.flags[rank] + TCCL_FLAG_TREE_DACK + ((tree * TCCL_TREE_MAX_CTAS + k) * 2 + slot);
   }
   // ring slot of (tree, child slot, cta, chunk sequence number) in `rank`'s memory
   static __device__ __forceinline__ char* ring(const tccl_comm& c, int rank, int tree, int cslot, int k, uint32_t seq) {
@@ -106,20 +109,6 @@ struct TreeAllReduce {
     const uint32_t base = *seq_word;  // chunks this pipeline has moved in earlier calls
     const int cslot = a.child_slot[tree];
 
-    __shared__ __align__(128) uint8_t s_buf[kBulk ? 2 : 1][kBulk ? kSub * 16 : 16];
-    __shared__ uint64_t s_bar[2];
-    __shared__ int s_abort;
-    uint32_t s_phase = 0;  // (thread 0) parity of the two load barriers
-    if (kBulk) {
-      if (t == 0) {
-        s_abort = 0;
-        gemm::mbar_init(s_bar + 0, 1);
-        gemm::mbar_init(s_bar + 1, 1);
-        gemm::fence_barrier_init();
-      }
-      __syncthreads();
-    }
-
     bool ok = true;
     if (is_up) {
       for (uint64_t n = 0; n < mine && ok; ++n) {
@@ -138,48 +127,6 @@ struct TreeAllReduce {
         const char* lring = left >= 0 ? ring(c, me, tree, 0, k, g) : nullptr;
         const char* rring = right >= 0 ? ring(c, me, tree, 1, k, g) : nullptr;
         char* pring = parent >= 0 ? ring(c, parent, tree, cslot, k, g) : nullptr;
-        if (kBulk) {
-          uint32_t sub = 0;
-          for (uint64_t s0 = lo; s0 < hi; s0 += kSub, ++sub) {
-            uint8_t* buf = s_buf[sub & 1];
-            const uint32_t cnt = (uint32_t)min((uint64_t)kSub, hi - s0);
-            if (sub >= 2) {
-              if (t == 0) gemm::bulk_wait_read<1>();  // the copies of two pieces ago have read this buffer
-              __syncthreads();
-            }
-            for (uint32_t j = t; j < cnt; j += nt) {
-              const uint64_t i = s0 + j;
-              Vec16 r = ld_peer(in + i * 16);
-              if (lring) {
-                Acc<T> acc;
-                acc.zero();
-                acc.add(r);
-                acc.add(ld_peer(lring + (i - lo) * 16));
-                if (rring) acc.add(ld_peer(rring + (i - lo) * 16));
-                r = acc.pack();
-              }
-              gemm::st_shared_v4(buf + (size_t)j * 16, r);
-            }
-            gemm::fence_proxy_async_smem();  // generic-proxy writes -> visible to the bulk copies
-            __syncthreads();
-            if (t == 0) {
-              const uint32_t bytes = cnt * 16;
-              if (pring) {
-                gemm::bulk_store(pring + (s0 - lo) * 16, buf, bytes);
-              } else {  // the root: the final value goes to its own and its children's result buffers
-                gemm::bulk_store(res + s0 * 16, buf, bytes);
-                if (lres) gemm::bulk_store(lres + s0 * 16, buf, bytes);
-                if (rres) gemm::bulk_store(rres + s0 * 16, buf, bytes);
-                if (out) gemm::bulk_store(out + s0 * 16, buf, bytes);
-              }
-              gemm::bulk_commit();
-            }
-          }
-          if (t == 0) {
-            gemm::bulk_wait<0>();  // complete, not just read out of shared memory, before the flags go up
-            gemm::fence_proxy_async();
-          }
-        } else
         for (uint64_t i0 = lo + t; i0 < hi; i0 += (uint64_t)U * nt) {
           Vec16 vo[U], vl[U], vr[U];
 #pragma unroll
@@ -208,8 +155,10 @@ struct TreeAllReduce {
                 st_peer(pring + (i - lo) * 16, r);
               } else {  // the root: this is the final value
                 st_peer(res + i * 16, r);
-                if (lres) st_peer(lres + i * 16, r);
-                if (rres) st_peer(rres + i * 16, r);
+                if (!kPullDown) {
+                  if (lres) st_peer(lres + i * 16, r);
+                  if (rres) st_peer(rres + i * 16, r);
+                }
                 if (out) st_local(out + i * 16, r);
               }
             }
@@ -228,72 +177,57 @@ struct TreeAllReduce {
           if (right >= 0) st_release_sys(ack_flag(c, right, tree, k), g + 1u);
         }
       }
-    } else if (parent >= 0) {
-      for (uint64_t n = 0; n < mine && ok; ++n) {
+    } else {
+      const char* pres = parent >= 0 ? reinterpret_cast<const char*>(a.buf[parent]) : nullptr;
+      for (uint64_t n = 0; parent >= 0 && n < mine && ok; ++n) {
         const uint32_t g = base + (uint32_t)n;
         if (t == 0) ok = wait_reach(down_flag(c, me, tree, k), g + 1u, c, deadline, parent, TCCL_W_TREE_DOWN);
         ok = __syncthreads_and(ok);
         if (!ok) break;
-        if (lres || out) {
+        if (kPullDown || lres || out) {
           const uint64_t clo = (2 * n + tree) * cv, chi = min(clo + cv, nvec);
           const uint64_t per = (chi - clo + K - 1) / K, lo = min(clo + per * k, chi), hi = min(lo + per, chi);
           constexpr int UD = 8;
-          if (kBulk) {
-            if (t == 0) {
-              gemm::fence_proxy_async();  // the parent's data, seen through the acquire above, is read by bulk copies next
-              const uint32_t nsub = (uint32_t)((hi - lo + kSub - 1) / kSub);
-              auto issue = [&](uint32_t sb) {
-                const uint64_t s0 = lo + (uint64_t)sb * kSub;
-                const uint32_t bytes = (uint32_t)min((uint64_t)kSub, hi - s0) * 16;
-                gemm::mbar_arrive_expect_tx(s_bar + (sb & 1), bytes);
-                tree_bulk_load(s_buf[sb & 1], res + s0 * 16, bytes, s_bar + (sb & 1));
-              };
-              gemm::Abort ab{&s_abort, &c, c.local + TCCL_LOCAL_STATUS, deadline};
-              if (nsub) issue(0);
-              for (uint32_t sb = 0; sb < nsub && ok; ++sb) {
-                if (sb + 1 < nsub) {
-                  gemm::bulk_wait_read<0>();  // the stores that last used the other buffer have read it
-                  issue(sb + 1);
-                }
-                ok = gemm::mbar_wait(s_bar + (sb & 1), (s_phase >> (sb & 1)) & 1u, ab);
-                if (!ok) break;
-                s_phase ^= 1u << (sb & 1);
-                const uint64_t s0 = lo + (uint64_t)sb * kSub;
-                const uint32_t bytes = (uint32_t)min((uint64_t)kSub, hi - s0) * 16;
-                if (lres) gemm::bulk_store(lres + s0 * 16, s_buf[sb & 1], bytes);
-                if (rres) gemm::bulk_store(rres + s0 * 16, s_buf[sb & 1], bytes);
-                if (out) gemm::bulk_store(out + s0 * 16, s_buf[sb & 1], bytes);
-                gemm::bulk_commit();
-              }
-              gemm::bulk_wait<0>();
-              gemm::fence_proxy_async();
-            }
-            ok = __syncthreads_and(ok);
-            if (!ok) break;
-          } else
+          // pull: the slice is in the PARENT's result buffer; push: it is already in the own one
+          const char* src = kPullDown ? pres : res;
           for (uint64_t i0 = lo + t; i0 < hi; i0 += (uint64_t)UD * nt) {
             Vec16 v[UD];
 #pragma unroll
             for (int u = 0; u < UD; ++u) {
               const uint64_t i = i0 + (uint64_t)u * nt;
-              if (i < hi) v[u] = ld_peer(res + i * 16);
+              if (i < hi) v[u] = ld_peer(src + i * 16);
             }
 #pragma unroll
             for (int u = 0; u < UD; ++u) {
               const uint64_t i = i0 + (uint64_t)u * nt;
               if (i < hi) {
-                if (lres) st_peer(lres + i * 16, v[u]);
-                if (rres) st_peer(rres + i * 16, v[u]);
+                if (kPullDown) {
+                  st_peer(res + i * 16, v[u]);  // own buffer: the children pull it from here
+                } else {
+                  if (lres) st_peer(lres + i * 16, v[u]);
+                  if (rres) st_peer(rres + i * 16, v[u]);
+                }
                 if (out) st_local(out + i * 16, v[u]);
               }
             }
           }
-          __syncthreads();
+          __syncthreads();  // every thread's loads are complete (their values were stored) and its stores issued
           if (t == 0) {
             if (left >= 0) st_release_sys(down_flag(c, left, tree, k), g + 1u);
             if (right >= 0) st_release_sys(down_flag(c, right, tree, k), g + 1u);
+          } else if (t == 1 && kPullDown) {
+            st_release_sys(dack_flag(c, parent, tree, k, cslot), g + 1u);  // this slice of the parent's buffer is no longer needed
           }
         }
+      }
+      if (kPullDown && ok && mine) {
+        // nobody may still be loading from this rank's result buffer when the kernel returns
+        if (t < 2) {
+          const int kid = t == 0 ? left : right;
+          if (kid >= 0)
+            ok = wait_reach(dack_flag(c, me, tree, k, t), base + (uint32_t)mine, c, deadline, kid, TCCL_W_TREE_DOWN);
+        }
+        ok = __syncthreads_and(ok);
       }
     }
     if (ok && t == 0) *seq_word = base + (uint32_t)mine;
@@ -313,7 +247,7 @@ extern "C" int tccl_allreduce_tree(const tccl_comm* comm, const tccl_tree_args* 
     if (K < 1 || K > tree_max_ctas(comm->tree_bytes) || l->grid != 4 * K) return -TCCL_ESIZE;
     if (args->chunk_vecs < 1 || args->chunk_vecs > (uint64_t)K * (TCCL_TREE_SLICE_BYTES / 16)) return -TCCL_ESIZE;
   }
-  if (l->meta & TCCL_TREE_BULK) {  // large messages: the copy engine carries the data
+  if (l->meta & TCCL_TREE_PULL_DOWN) {  // large messages: children load the sum from their parent
     switch (dtype) {
       case TCCL_BF16: return launch_op<TreeAllReduce<__nv_bfloat16, true>>(comm, args, l);
       case TCCL_F32: return launch_op<TreeAllReduce<float, true>>(comm, args, l);

@@ -226,7 +226,7 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.comm_ctas = comm_ctas
         g.swiglu = 1 if swiglu else 0
         g.trace = _trace_ptr(w, trace, r, grid)
-        g.lsu_movers = 1 if lsu_movers else 0
+        g.lsu_movers = int(lsu_movers)  # pair kernel: 2 = move the shard only (timeline tool)
         arr[i] = g
     stream = torch.cuda.current_stream(a0.device).cuda_stream
     if pair:

@@ -102,8 +102,8 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
             _check_out(o, w.local(x, r))
             a.out = o.data_ptr()
         args[r] = a
-    bulk = K["TCCL_TREE_BULK"] if nbytes >= w.config.tree_bulk_min_bytes else 0
-    go = w.prepare("tccl_allreduce_tree", args, 4 * k, w.config.block, dt | bulk)
+    pull = K["TCCL_TREE_PULL_DOWN"] if nbytes >= w.config.tree_pull_min_bytes else 0
+    go = w.prepare("tccl_allreduce_tree", args, 4 * k, w.config.block, dt | pull)
     if out is not None:
         return Plan(w, go, args, result=_OUT)
     if inplace:

@@ -27,7 +27,7 @@ class HpTree(C.Structure):
     _fields_ = [("inp", C.c_uint64), ("buf", C.c_uint64 * MAXW), ("ring", C.c_uint64 * MAXW),
                 ("numel", C.c_uint64), ("chunk", C.c_uint64), ("ring_stride", C.c_uint64),
                 ("parent", C.c_int32 * 2), ("left", C.c_int32 * 2), ("right", C.c_int32 * 2),
-                ("child_slot", C.c_int32 * 2)]
+                ("child_slot", C.c_int32 * 2), ("pull_down", C.c_int32), ("pad_", C.c_int32)]
 
 
 def _lib(path: Optional[str] = None) -> C.CDLL:
@@ -89,6 +89,7 @@ def _rank_main(lib_path: str, shm_name: str, world: int, rank: int, numel: int, 
                 t.ring[p] = base + rings[p]
             t.numel, t.chunk = numel, int(faults.get("chunk", max(1, numel // 16)))
             t.ring_stride = numel
+            t.pull_down = int(faults.get("pull_down", 0))
             for tr in (0, 1):
                 parent, left, right = tree_neighbours(world, rank, tr)
                 t.parent[tr], t.left[tr], t.right[tr] = parent, left, right

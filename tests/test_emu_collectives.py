@@ -328,29 +328,33 @@ def test_double_tree_all_reduce(emu_worlds, W, dtype, n, chunk_kb, ll):
 @pytest.mark.parametrize("W", [1, 2, 3, 8])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("n", [4096 + 8, (1 << 20) + 64, 3 << 20])
-def test_double_tree_bulk_copy_path(emu_worlds, W, dtype, n):
-    """The large-message data path (sums staged in shared memory, moved by bulk async copies), forced
-    on for sizes that end pieces and slices at odd places; same bits as the store path."""
+def test_double_tree_push_and_pull_down_agree(emu_worlds, W, dtype, n):
+    """The two forms of the way down (parents store into their children / children load from their
+    parent and acknowledge) give the same bits, out of place and in place, twice in a row."""
     import tccl_b200 as tccl
 
     w = emu_worlds(W)
-    old = (w.config.tree_bulk_min_bytes, w.config.tree_ll_max_bytes)
+    old = (w.config.tree_pull_min_bytes, w.config.tree_ll_max_bytes)
     try:
         x = make_inputs(w, W, n, dtype, 2500)
         keep = [p.clone() for p in x.parts]
         w.config.tree_ll_max_bytes = 0
-        w.config.tree_bulk_min_bytes = 1 << 40
-        plain = tccl.double_tree_all_reduce(x, world=w)
-        w.config.tree_bulk_min_bytes = 0
-        bulk = tccl.double_tree_all_reduce(x, world=w)
-        y = w.from_parts([p.clone() for p in keep])
-        tccl.all_reduce(y, inplace=True, algo="tree", world=w)
+        w.config.tree_pull_min_bytes = 1 << 40
+        push = tccl.double_tree_all_reduce(x, world=w)
+        w.config.tree_pull_min_bytes = 0
+        pull = tccl.double_tree_all_reduce(x, world=w)
+        ys = []
+        for _ in range(2):
+            y = w.from_parts([p.clone() for p in keep])
+            tccl.all_reduce(y, inplace=True, algo="tree", world=w)
+            ys.append(y)
         torch.cuda.synchronize()
         w.check()
         for r in range(W):
-            assert torch.equal(bulk[r], plain[r]) and torch.equal(y[r], plain[r]) and torch.equal(x[r], keep[r])
+            assert torch.equal(pull[r], push[r]) and torch.equal(x[r], keep[r])
+            assert torch.equal(ys[0][r], push[r]) and torch.equal(ys[1][r], push[r])
     finally:
-        w.config.tree_bulk_min_bytes, w.config.tree_ll_max_bytes = old
+        w.config.tree_pull_min_bytes, w.config.tree_ll_max_bytes = old
 
 
 @pytest.mark.parametrize("W", [2, 4, 8])

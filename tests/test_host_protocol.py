@@ -16,11 +16,13 @@ def test_barrier_many_rounds():
     assert all(v["ok"] == 1 and v["status"]["code"] == 0 for v in res.values())
 
 
+@pytest.mark.parametrize("pull_down", [0, 1])
 @pytest.mark.parametrize("W", [2, 4, 8])
-def test_tree_allreduce_on_cpu_ranks(W):
+def test_tree_allreduce_on_cpu_ranks(W, pull_down):
     n = 1 << 14
     xs = [np.random.default_rng(r).standard_normal(n).astype(np.float32) for r in range(W)]
-    res, outs = run_ranks(W, "tree", numel=n, inputs=xs, faults={r: {"chunk": 1 << 9} for r in range(W)})
+    res, outs = run_ranks(W, "tree", numel=n, inputs=xs,
+                          faults={r: {"chunk": 1 << 9, "pull_down": pull_down} for r in range(W)})
     assert all(v["ok"] == 1 for v in res.values()), res
     ref = np.sum(np.stack(xs).astype(np.float64), 0)
     for o in outs:
@@ -50,15 +52,16 @@ def test_rank_that_never_joins():
         assert res[r]["ok"] == 0 and st["code"] == 1 and st["peer"] == 2
 
 
-def test_rank_that_stops_mid_all_reduce():
+@pytest.mark.parametrize("pull_down", [0, 1])
+def test_rank_that_stops_mid_all_reduce(pull_down):
     """Rank 2 stops after three chunks: its tree neighbours time out in the up or
     down phase, everybody returns, nobody hangs."""
     W, n = 4, 1 << 14
     xs = [np.ones(n, np.float32) * r for r in range(W)]
     t0 = time.time()
     res, _ = run_ranks(W, "tree", numel=n, inputs=xs, timeout_ms=400,
-                       faults={r: ({"chunk": 1 << 9, "stop_after_chunk": 3} if r == 2 else {"chunk": 1 << 9})
-                               for r in range(W)})
+                       faults={r: ({"chunk": 1 << 9, "pull_down": pull_down, "stop_after_chunk": 3} if r == 2
+                                   else {"chunk": 1 << 9, "pull_down": pull_down}) for r in range(W)})
     assert time.time() - t0 < 30
     failed = [r for r in range(W) if res[r]["ok"] == 0]
     assert failed, res

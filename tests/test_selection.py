@@ -67,7 +67,7 @@ def test_tree_grid_fits_the_ring_and_scales_ctas_with_the_message():
     w = StubWorld(8, True)
     slice_vecs = K["TCCL_TREE_SLICE_BYTES"] // 16
     k, vecs = _tree_grid(w, 1 << 30)
-    assert k == 32 and vecs == k * slice_vecs          # large: every CTA moves a full ring slice per chunk
+    assert k == w.config.tree_ctas == 36 and vecs == k * slice_vecs  # large: every CTA moves a full ring slice per chunk
     k, vecs = _tree_grid(w, 1 << 20)
     assert k == 16 and vecs <= k * slice_vecs and (1 << 20) // 2 // (vecs * 16) >= 4  # >= 4 chunks per tree
     k, vecs = _tree_grid(w, 4096)
