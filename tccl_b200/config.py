@@ -42,12 +42,13 @@ class Config:
     oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
     staged_twoshot: bool = True           # large all-reduce into ordinary memory: two-shot via a cached symmetric buffer
     staged_max_bytes: int = 1 << 30       # ... up to this message size (the buffer is kept per size and dtype)
-    tree_chunk_bytes: int = 4 * 1024 * 1024  # double-tree: bytes per chunk (per tree)
+    tree_chunk_bytes: int = 16 << 20      # double-tree: most bytes per chunk (a chunk = one ring slice per CTA of a tree)
     tree_ctas: int = 36                   # double-tree: CTAs per (tree, direction); 4 x 36 = 144 of 148 SMs
     tree_ll_max_bytes: int = 2 << 20      # double-tree: up to here the flags travel inside the data lines
     tree_pull_min_bytes: int = 0          # double-tree, chunked kernel: from here on children pull the sum from the parent
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
+    ag_batches: int = 2                   # all-gather -> GEMM on CTA pairs: batches the shard goes out in (one fence each)
     plan_cache_size: int = 512            # bound launches kept per communicator (least recently used go first)
     debug: bool = False
     debug_shrink_extent: int = 0          # test hook of the TCCL_DEBUG_CHECKS build: claim this many bytes less input

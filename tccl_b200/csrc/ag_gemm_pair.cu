@@ -5,7 +5,7 @@
 // What differs from the single-CTA form (ag_gemm.cu):
 //  * No CTA is set aside to move data.  The four epilogue warps of EVERY CTA open
 //    as data movers while the producer and MMA warps already compute on the
-//    rank's own rows: in two batches of row tiles each CTA stores its 1/grid
+//    rank's own rows: in a few batches of row tiles each CTA stores its 1/grid
 //    share of the shard into the gathered buffer of every rank (one multimem.st
 //    per vector through the switch when NVLS is there, else one posted store per
 //    peer), and the CTA that completes a batch raises the flags of its row tiles
@@ -39,6 +39,7 @@ struct alignas(64) AgGemmPairParams {
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank;
   int swiglu;
+  int batches;      // batches the shard's row tiles go out in (each ends in one system-scope fence)
   int movers_only;  // diagnostic (timeline tool): move the shard, compute nothing
   uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
 };
@@ -79,7 +80,7 @@ struct AgGemmPairPolicy {
 
   // The data-mover phase, run by the four epilogue warps of EVERY CTA while the producer and MMA
   // warps already work on the rank's own rows (the first accumulator is tens of microseconds
-  // away).  The shard's row tiles go out in two batches; in each, CTA b stores its 1/grid share of
+  // away).  The shard's row tiles go out in `batches` batches; in each, CTA b stores its 1/grid share of
   // every row tile into the gathered buffer of every rank, and the CTA that completes a batch
   // raises the flags of its row tiles on every rank.  One system-scope fence per batch: a fence
   // per row tile would cost a switch round trip each and hold back the whole kernel.
@@ -92,7 +93,7 @@ struct AgGemmPairPolicy {
     const uint32_t nvec = 128u * (uint32_t)vec_per_row;
     const uint32_t per = (nvec + nb - 1) / nb;
     const uint32_t lo = min(per * (uint32_t)bid, nvec), hi = min(lo + per, nvec);
-    const int nbatch = p->tiles_m_per_rank >= 2 ? 2 : 1;
+    const int nbatch = max(1, min(p->batches, p->tiles_m_per_rank));
     for (int b = 0; b < nbatch; ++b) {
       const int rt0 = b * p->tiles_m_per_rank / nbatch, rt1 = (b + 1) * p->tiles_m_per_rank / nbatch;
       for (int rt = rt0; rt < rt1; ++rt) {
@@ -123,9 +124,9 @@ struct AgGemmPairPolicy {
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // this CTA's share of the batch is stored
       if (t == 0) {
-        if (trace) trace[60 - 2 * b] = globaltimer();
+        if (trace && b < 2) trace[60 - 2 * b] = globaltimer();
         fence_acq_rel_sys();
-        if (trace) trace[59 - 2 * b] = globaltimer();
+        if (trace && b < 2) trace[59 - 2 * b] = globaltimer();
         const uint32_t done = atomicAdd(c->local + TCCL_LOCAL_AGCNT + b, 1u);
         *s_last = (done == (uint32_t)nb - 1u);
         if (*s_last) {
@@ -282,6 +283,7 @@ static int fill_params(AgGemmPairParams* p, const tccl_ag_gemm_args* g, int worl
   p->tiles_n = (g->n + BN2 - 1) / BN2;
   p->tiles_m_per_rank = rows / 128;
   p->swiglu = g->swiglu;
+  p->batches = g->comm_ctas > 0 ? g->comm_ctas : 2;
   p->movers_only = g->lsu_movers == 2;
   p->trace = reinterpret_cast<uint64_t*>(g->trace);
   if (g->swiglu && (g->n % BN2)) return -TCCL_ESIZE;  // whole gate|up tiles only
@@ -297,8 +299,9 @@ using namespace tccl::gemm2;
 
 extern "C" uint64_t tccl_ag_gemm_pair_param_bytes(void) { return sizeof(AgGemmPairParams); }
 
-// Same calling convention as tccl_allgather_gemm (comm_ctas and lsu_movers of the arguments are not
-// used: every CTA moves data first).  `half_bytes`: distance in bytes from a_full[q] to the second
+// Same calling convention as tccl_allgather_gemm, except that every CTA moves data first: comm_ctas of
+// the arguments is the number of batches the shard goes out in (0 = 2), lsu_movers == 2 the diagnostic
+// "move only".  `half_bytes`: distance in bytes from a_full[q] to the second
 // half of every rank's gathered buffer, or 0 when there is only one buffer (then the kernel opens
 // with a barrier).  l->grid must be even.
 extern "C" int tccl_allgather_gemm_pair(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,

@@ -97,11 +97,13 @@ typedef struct tccl_comm {
 } tccl_comm;
 
 /* double-tree ring.  First the small-message (flag-in-line) part: slots [tree][left, right, down][cta][seq % depth];
- * then the chunked part: slots [tree][child slot][cta][chunk % depth].  Every slot is TCCL_TREE_SLICE_BYTES long. */
-#define TCCL_TREE_SLICE_BYTES 65536
+ * of TCCL_TREE_LL_SLOT_BYTES each; then the chunked part: slots [tree][child slot][cta][chunk % depth] of
+ * TCCL_TREE_SLICE_BYTES each (large slices: the cost of a slice's flag traffic and release fence is per slice). */
+#define TCCL_TREE_SLICE_BYTES 262144
+#define TCCL_TREE_LL_SLOT_BYTES 65536
 #define TCCL_TREE_RING_DEPTH 4
 #define TCCL_TREE_LL_MAX_CTAS 32
-#define TCCL_TREE_LL_BYTES (2 * 3 * TCCL_TREE_LL_MAX_CTAS * TCCL_TREE_RING_DEPTH * TCCL_TREE_SLICE_BYTES)
+#define TCCL_TREE_LL_BYTES (2 * 3 * TCCL_TREE_LL_MAX_CTAS * TCCL_TREE_RING_DEPTH * TCCL_TREE_LL_SLOT_BYTES)
 
 /* Arguments shared by the data collectives. */
 typedef struct tccl_coll_args {

@@ -166,15 +166,17 @@ struct TreeAllReduce {
         }
         __syncthreads();  // every thread has used what it loaded and issued its stores
         if (t == 0) {
+          // ONE release fence (it waits until the CTA's stores have been performed; a per-flag
+          // st.release would pay that once per flag), then the counters as relaxed stores
+          fence_acq_rel_sys();
           if (parent >= 0) {
-            st_release_sys(up_flag(c, parent, tree, k, cslot), g + 1u);
+            st_relaxed_sys(up_flag(c, parent, tree, k, cslot), g + 1u);
           } else {
-            if (left >= 0) st_release_sys(down_flag(c, left, tree, k), g + 1u);
-            if (right >= 0) st_release_sys(down_flag(c, right, tree, k), g + 1u);
+            if (left >= 0) st_relaxed_sys(down_flag(c, left, tree, k), g + 1u);
+            if (right >= 0) st_relaxed_sys(down_flag(c, right, tree, k), g + 1u);
           }
-        } else if (t == 1) {
-          if (left >= 0) st_release_sys(ack_flag(c, left, tree, k), g + 1u);
-          if (right >= 0) st_release_sys(ack_flag(c, right, tree, k), g + 1u);
+          if (left >= 0) st_relaxed_sys(ack_flag(c, left, tree, k), g + 1u);
+          if (right >= 0) st_relaxed_sys(ack_flag(c, right, tree, k), g + 1u);
         }
       }
     } else {
@@ -213,10 +215,11 @@ struct TreeAllReduce {
           }
           __syncthreads();  // every thread's loads are complete (their values were stored) and its stores issued
           if (t == 0) {
-            if (left >= 0) st_release_sys(down_flag(c, left, tree, k), g + 1u);
-            if (right >= 0) st_release_sys(down_flag(c, right, tree, k), g + 1u);
-          } else if (t == 1 && kPullDown) {
-            st_release_sys(dack_flag(c, parent, tree, k, cslot), g + 1u);  // this slice of the parent's buffer is no longer needed
+            fence_acq_rel_sys();
+            if (left >= 0) st_relaxed_sys(down_flag(c, left, tree, k), g + 1u);
+            if (right >= 0) st_relaxed_sys(down_flag(c, right, tree, k), g + 1u);
+            // pull: this slice of the parent's buffer is no longer needed
+            if (kPullDown) st_relaxed_sys(dack_flag(c, parent, tree, k, cslot), g + 1u);
           }
         }
       }

@@ -29,8 +29,8 @@
 namespace tccl {
 
 constexpr int kLLDepth = TCCL_TREE_RING_DEPTH;
-constexpr uint64_t kLLSlot = TCCL_TREE_SLICE_BYTES;       // bytes per slot
-constexpr uint32_t kLLLines = TCCL_TREE_SLICE_BYTES / 16;  // lines per slot, 8 payload bytes each
+constexpr uint64_t kLLSlot = TCCL_TREE_LL_SLOT_BYTES;      // bytes per slot
+constexpr uint32_t kLLLines = TCCL_TREE_LL_SLOT_BYTES / 16;  // lines per slot, 8 payload bytes each
 
 template <typename T>
 struct TreeAllReduceLL {
@@ -179,7 +179,7 @@ extern "C" int tccl_allreduce_tree_ll(const tccl_comm* comm, const tccl_tree_arg
     const uint64_t esz = args->dtype == TCCL_F32 ? 4 : 2;
     if (K < 1 || K > TCCL_TREE_LL_MAX_CTAS || l->grid != 4 * K) return -TCCL_ESIZE;
     if (comm->tree_bytes < TCCL_TREE_LL_BYTES) return -TCCL_ESIZE;
-    if (args->numel * esz > 2ull * K * (TCCL_TREE_SLICE_BYTES / 2) || (args->numel * esz) % 16) return -TCCL_ESIZE;
+    if (args->numel * esz > 2ull * K * (TCCL_TREE_LL_SLOT_BYTES / 2) || (args->numel * esz) % 16) return -TCCL_ESIZE;
   }
   switch (dtype) {
     case TCCL_BF16: return launch_op<TreeAllReduceLL<__nv_bfloat16>>(comm, args, l);

@@ -193,7 +193,8 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
                 from ..parallel.emu import EmuTensor
                 ret_full = EmuTensor([t[seq & 1] for t in a_full.parts])
     full_ptrs = w.peer_ptrs(a_full)
-    mc = w.mc_ptr(a_full)
+    # two ranks: the switch would deliver every row to its sender too (twice the inbound bytes of a plain store)
+    mc = w.mc_ptr(a_full) if (W > 2 or not pair) else 0
     lib = L.lib()
     lib.tccl_ag_gemm_param_bytes.restype = C.c_uint64
     lib.tccl_ag_gemm_pair_param_bytes.restype = C.c_uint64
@@ -223,7 +224,7 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.bt, g.out = br.data_ptr(), o.data_ptr()
         g.m, g.n, g.k = M, N, Kd
         g.lda_shard, g.lda_full, g.ldb, g.ldo = ar.stride(0), Kd, br.stride(0), o.stride(0)
-        g.comm_ctas = comm_ctas
+        g.comm_ctas = max(1, int(w.config.ag_batches)) if pair else comm_ctas  # pair kernel: batches of the mover phase
         g.swiglu = 1 if swiglu else 0
         g.trace = _trace_ptr(w, trace, r, grid)
         g.lsu_movers = int(lsu_movers)  # pair kernel: 2 = move the shard only (timeline tool)

@@ -32,6 +32,7 @@ from .collectives import _OUT, _X, Plan, _cached, _check_out, _key
 __all__ = ["double_tree_all_reduce"]
 
 _SLICE = K["TCCL_TREE_SLICE_BYTES"]
+_LL_SLOT = K["TCCL_TREE_LL_SLOT_BYTES"]
 
 
 def _tree_grid(w: WorldBase, nbytes: int):
@@ -65,7 +66,7 @@ def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:
     if nbytes % 16:
         raise ValueError("the element count must be a whole number of 16-byte vectors")
     W = w.world_size
-    if nbytes <= min(w.config.tree_ll_max_bytes, 2 * _ll_max_ctas(w) * (_SLICE // 2)):
+    if nbytes <= min(w.config.tree_ll_max_bytes, 2 * _ll_max_ctas(w) * (_LL_SLOT // 2)):
         return _plan_ll(w, x, out, inplace, x0, dt, nbytes)
     if inplace:
         # parents store the sum into their children's result buffer: it must be peer-mapped
@@ -132,7 +133,7 @@ def _plan_ll(w: WorldBase, x, out, inplace: bool, x0, dt: int, nbytes: int) -> P
     come back through the ring too, so the result is written locally and nothing needs a scratch."""
     W = w.world_size
     k = max(1, min(_ll_max_ctas(w), -(-nbytes // 16384)))
-    while 2 * k * (_SLICE // 2) < nbytes:
+    while 2 * k * (_LL_SLOT // 2) < nbytes:
         k += 1
     args = {}
     for r in w.local_ranks:
