@@ -49,6 +49,9 @@ class Config:
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
     ag_batches: int = 2                   # all-gather -> GEMM on CTA pairs: batches the shard goes out in (one fence each)
+    ag_schedule: bool = True              # ... its tiles follow a host-made plan (list scheduling against the rows' arrival)
+    ag_pair_tflops: float = 20.0          # ... cost model of that plan: bf16 TFLOP/s of one CTA pair,
+    ag_link_gbs: float = 600.0            # ... and GB/s at which the peers' rows arrive
     plan_cache_size: int = 512            # bound launches kept per communicator (least recently used go first)
     debug: bool = False
     debug_shrink_extent: int = 0          # test hook of the TCCL_DEBUG_CHECKS build: claim this many bytes less input

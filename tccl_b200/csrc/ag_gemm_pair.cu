@@ -29,7 +29,7 @@ namespace tccl {
 namespace gemm2 {
 
 struct alignas(64) AgGemmPairParams {
-  CUtensorMap map_a_shard, map_a_full[2], map_b;
+  CUtensorMap map_a_shard, map_a_full[2], map_b, map_b64;
   Shape shp;
   const char* a_shard;
   char* a_full[TCCL_MAX_WORLD];  // every rank's gathered buffer (half 0)
@@ -39,6 +39,8 @@ struct alignas(64) AgGemmPairParams {
   int lda_shard, lda_full, ldo;
   int tiles_n, tiles_m_per_rank;
   int swiglu;
+  const int32_t* sched;  // optional: every pair's tiles in running order (see tccl_ag_gemm_args)
+  int sched_stride;
   int batches;      // batches the shard's row tiles go out in (each ends in one system-scope fence)
   int movers_only;  // diagnostic (timeline tool): move the shard, compute nothing
   uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
@@ -54,11 +56,21 @@ struct AgGemmPairPolicy {
   uint64_t* trace;  // this CTA's trace words, or null: [60 - 2 b] batch b stored, [59 - 2 b] batch b fenced
 
   __device__ __forceinline__ bool tile(int i, int& mt, int& nt, int& half) const {
+    if (p->movers_only) return false;
+    if (p->sched) {  // the host's plan for this pair
+      if (i >= p->sched_stride) return false;
+      const int32_t v = __ldg(p->sched + (size_t)pair * p->sched_stride + i);
+      if (v < 0) return false;
+      mt = v & 0xfff;
+      nt = (v >> 12) & 0xffff;
+      half = (v >> 28) & 3;
+      return true;
+    }
     const int t = pair + i * npairs;
     const int tm2 = p->tiles_m_per_rank / 2, tn = p->tiles_n, W = c->world;
     const int own = tm2 * tn;
     half = 0;
-    if (t >= W * own || p->movers_only) return false;
+    if (t >= W * own) return false;
     if (t < own) {  // own rows first: no waiting
       mt = c->rank * p->tiles_m_per_rank + 2 * (t / tn);
       nt = t % tn;
@@ -74,7 +86,11 @@ struct AgGemmPairPolicy {
     nt = v % tn;
     return true;
   }
-  __device__ __forceinline__ const CUtensorMap* map_b(int) const { return &p->map_b; }
+  __device__ __forceinline__ void b_tile(int nt, int half, int cta, const CUtensorMap*& map, int& y) const {
+    map = half ? &p->map_b64 : &p->map_b;
+    // gate | up packing: a half tile is 64 gate columns (CTA 0) and the 64 matching up columns (CTA 1)
+    y = (p->swiglu && half) ? nt * BN2 + cta * 128 + (half == 2 ? 64 : 0) : b_rows_default(nt, half, cta);
+  }
   __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
   __device__ __forceinline__ void between_tiles(int, int, const Abort&) const {}
 
@@ -163,19 +179,21 @@ struct AgGemmPairPolicy {
       y = mt * 128;
     }
   }
-  __device__ __forceinline__ bool epilogue(int mt, int nt, int, int, uint32_t taddr, int quad, int lane, const Abort&,
-                                           const Smem2&) const {
+  __device__ __forceinline__ bool epilogue(int mt, int nt, int col_lo, int ncols, uint32_t taddr, int quad, int lane,
+                                           const Abort&, const Smem2&) const {
     const int row = mt * 128 + quad * 32 + lane;
     __nv_bfloat16* crow = p->out + (size_t)row * p->ldo;
     if (p->swiglu) {
-      // every 256-wide tile holds 128 gate columns followed by the 128 matching up columns
+      // every 256-wide tile holds 128 gate columns followed by the 128 matching up columns; a half
+      // tile's accumulator holds 64 of each (see b_tile)
+      const int hw = ncols / 2;
 #pragma unroll 1
-      for (int cg = 0; cg < BN2 / 64; ++cg) {
+      for (int cg = 0; cg < hw / 32; ++cg) {
         uint32_t g[32], u[32];
         tmem_ld_32x32(taddr + cg * 32, g);
-        tmem_ld_32x32(taddr + BN2 / 2 + cg * 32, u);
+        tmem_ld_32x32(taddr + hw + cg * 32, u);
         tmem_ld_wait();
-        const int col0 = nt * (BN2 / 2) + cg * 32;
+        const int col0 = nt * (BN2 / 2) + col_lo / 2 + cg * 32;
         if (row < p->shp.M) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -194,11 +212,11 @@ struct AgGemmPairPolicy {
       return true;
     }
 #pragma unroll 1
-    for (int cg = 0; cg < BN2 / 32; ++cg) {
+    for (int cg = 0; cg < ncols / 32; ++cg) {  // a half tile's 128 columns sit at the start of the accumulator
       uint32_t r[32];
       tmem_ld_32x32(taddr + cg * 32, r);
       tmem_ld_wait();
-      const int col0 = nt * BN2 + cg * 32;
+      const int col0 = nt * BN2 + col_lo + cg * 32;
       if (row < p->shp.M) {
 #pragma unroll
         for (int v = 0; v < 4; ++v)
@@ -230,6 +248,7 @@ __device__ __forceinline__ void ag_gemm_pair_body(const tccl_comm& c, const AgGe
     tma_prefetch_desc(&p.map_a_shard);
     tma_prefetch_desc(&p.map_a_full[parity]);
     tma_prefetch_desc(&p.map_b);
+    tma_prefetch_desc(&p.map_b64);
   }
   run_mainloop2(p.shp, pol, &c, c.timeout_ns, p.trace ? p.trace + (size_t)bid * 64 : nullptr);
   __syncthreads();
@@ -271,6 +290,11 @@ static int fill_params(AgGemmPairParams* p, const tccl_ag_gemm_args* g, int worl
   }
   rc = make_tmap_bf16_kmajor(&p->map_b, g->bt, g->n, g->k, g->ldb, 128);
   if (rc) return rc;
+  rc = make_tmap_bf16_kmajor(&p->map_b64, g->bt, g->n, g->k, g->ldb, 64);  // half tiles: 64 rows of Bt per CTA
+  if (rc) return rc;
+  p->sched = g->sched;
+  p->sched_stride = g->sched_stride;
+  if (g->sched && g->sched_stride <= 0) return -TCCL_EINVAL;
   p->shp = Shape{g->m, g->n, g->k};
   p->a_shard = reinterpret_cast<const char*>(g->a_shard);
   for (int q = 0; q < TCCL_MAX_WORLD; ++q) p->a_full[q] = reinterpret_cast<char*>(g->a_full[q]);

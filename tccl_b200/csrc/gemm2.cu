@@ -63,7 +63,10 @@ struct PlainPolicy2 {
     mt = 2 * mt2;
     return true;
   }
-  __device__ __forceinline__ const CUtensorMap* map_b(int half) const { return half ? map_b64 : map_b128; }
+  __device__ __forceinline__ void b_tile(int nt, int half, int cta, const CUtensorMap*& map, int& y) const {
+    map = half ? map_b64 : map_b128;
+    y = b_rows_default(nt, half, cta);
+  }
   __device__ __forceinline__ bool before_load(int, int, const Abort&) const { return true; }
   __device__ __forceinline__ void a_tile(int mt, const CUtensorMap*& map, int& y) const {
     map = map_a;

@@ -80,7 +80,10 @@ struct GemmRsPairPolicy {
     half = 0;
     return true;
   }
-  __device__ __forceinline__ const CUtensorMap* map_b(int) const { return &p->map_b; }
+  __device__ __forceinline__ void b_tile(int nt, int half, int cta, const CUtensorMap*& map, int& y) const {
+    map = &p->map_b;
+    y = b_rows_default(nt, half, cta);
+  }
   __device__ __forceinline__ bool before_load(int, int, const Abort&) const { return true; }
   __device__ __forceinline__ void a_tile(int mt, const CUtensorMap*& map, int& y) const {
     map = &p->map_a;

@@ -116,7 +116,9 @@ struct Smem2 {
 // Hooks (Policy):
 //   tile(i, mt, nt, half)                  -> false when the PAIR is out of tiles; mt is even
 //   a_tile(mt, map, y)                     -> tensor map (box of 128 rows) and row coordinate of m tile mt
-//   map_b(half)                            -> tensor map of Bt: box of 128 rows for half == 0, of 64 rows else
+//   b_tile(nt, half, cta, map, y)          -> tensor map of Bt (box of 128 rows for half == 0, of 64 rows else) and
+//                                             the first Bt row CTA `cta` of the pair loads; b_rows_default() below
+//                                             is the plain layout (the pair's rows are consecutive)
 //   before_load(mt, nt, ab)                -> producer thread, before the CTA's first load of its m tile
 //   epilogue(mt, nt, col0, ncols, taddr, quad, lane, ab, sm)
 //                                          -> 4 epilogue warps of each CTA; columns [col0, col0 + ncols) of
@@ -127,6 +129,11 @@ struct Smem2 {
 // `trace` (optional, this CTA's 64 words of %globaltimer stamps): [63] kernel start, [62] side work of
 // epilogue_begin done, and for the CTA's i-th tile, i < 14 (words 56..61 belong to the policies): [4i] producer may load, [4i+1] accumulator
 // ready, [4i+2] epilogue done.
+// first Bt row of CTA `cta` for (n tile, half) when a tile's columns are 256 consecutive rows of Bt
+__device__ __forceinline__ int b_rows_default(int nt, int half, int cta) {
+  return nt * BN2 + (half == 2 ? 128 : 0) + cta * (half ? 64 : 128);
+}
+
 template <class Policy>
 __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* comm, uint64_t timeout_ns,
                               uint64_t* trace = nullptr) {
@@ -174,9 +181,10 @@ __device__ void run_mainloop2(const Shape shp, Policy& pol, const tccl_comm* com
         const CUtensorMap* map_a;
         int ya;
         pol.a_tile(mt, map_a, ya);
-        const CUtensorMap* map_b = pol.map_b(half);
         const int brows = half ? 64 : 128;  // Bt rows this CTA loads per k-block
-        const int yb = nt * BN2 + (half == 2 ? 128 : 0) + (int)cta * brows;
+        const CUtensorMap* map_b;
+        int yb;
+        pol.b_tile(nt, half, (int)cta, map_b, yb);
         const uint32_t stage_bytes = kA2 + (uint32_t)brows * BK2 * 2;
         for (int kb = 0; ok && kb < num_kb; ++kb, ++it) {
           const int s = it % kStages2;

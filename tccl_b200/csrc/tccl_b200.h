@@ -301,14 +301,20 @@ typedef struct tccl_ag_gemm_args {
                                        rows; out is [m, n / 2] = silu(gate) * up (n % 256 == 0) */
   void* trace;                      /* optional: grid * 64 uint64 words of per-tile %globaltimer stamps */
   int32_t lsu_movers;               /* 1: move the shard with LSU / multimem.st stores instead of bulk copies */
+  int32_t sched_stride;             /* pair kernel: entries per CTA pair in `sched` */
+  const int32_t* sched;             /* pair kernel, optional (device memory): the tiles of every CTA pair in the order
+                                       it runs them, [pairs][sched_stride] entries TCCL_AG_UNIT(mt, nt, half), ended
+                                       by -1; mt = even 128-row tile, half = 0 (256 columns) / 1 / 2 (left / right
+                                       128).  NULL: own rows first, then the peers' rows in arrival order */
 } tccl_ag_gemm_args;
+#define TCCL_AG_UNIT(mt, nt, half) ((int32_t)(mt) | ((int32_t)(nt) << 12) | ((int32_t)(half) << 28))
 uint64_t tccl_ag_gemm_param_bytes(void);
 /* same calling convention as tccl_gemm_reduce_scatter */
 int tccl_allgather_gemm(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,
                         const tccl_launch* l);
 
 /* Same product on CTA pairs (tcgen05.mma.cta_group::2); every CTA moves its share of the shard first
- * (comm_ctas / lsu_movers are not used).  m % (world * 256) == 0; l->grid even.  `half_bytes`: distance
+ * (comm_ctas = batches of that phase, 0 = 2; lsu_movers == 2 = move only).  m % (world * 256) == 0; l->grid even.  `half_bytes`: distance
  * from a_full[q] to the second half of every rank's gathered buffer — the halves alternate from call to
  * call and no entry barrier is needed — or 0 for a single buffer (the kernel then opens with a barrier). */
 uint64_t tccl_ag_gemm_pair_param_bytes(void);

@@ -130,6 +130,67 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, variant: str = "auto", w
     return [outs[r] for r in w.local_ranks] if w.plans is None else outs[w.local_ranks[0]]
 
 
+def ag_pair_schedule(W: int, rank: int, tm: int, tn: int, pairs: int, nbatch: int, k: int, *, halves: bool = True,
+                     pair_tflops: float = 20.0, link_gbs: float = 600.0, start_us: float = 8.0):
+    """Plan of the all-gather -> GEMM pair kernel: for every CTA pair the tiles it runs, in order.
+
+    The kernel's built-in order deals tile ``pair + i * pairs`` to a pair whatever the moment its rows
+    arrive; at 8 ranks most pairs then sit on a remote tile while others queue two tiles behind theirs.
+    This is list scheduling against a small cost model instead: the rank's own rows are there at once,
+    batch ``b`` of the peers' rows (``nbatch`` batches of ``tm / nbatch`` 128-row tiles per rank) after
+    ``start_us + (b + 1) / nbatch`` of the time the link needs for all of them, a 256 x 256 tile costs
+    ``2 * 256 * 256 * k / pair_tflops``.  Tiles are taken in the order their rows arrive and handed to
+    the pair that is free first; the last tiles (those of the last batch, one wave at most) are cut into
+    256 x 128 halves so that the work left when the last rows land spreads over all pairs.  Returns
+    ``pairs`` lists of ``(mt, nt, half)`` (``mt`` = even 128-row tile index, ``half`` 0 / 1 / 2 = whole
+    tile / left / right half).  Any plan that names every tile once is correct — the kernel waits for
+    the rows of whatever tile it is given — the model only decides how good it is."""
+    import heapq
+
+    tm2 = tm // 2
+    rows_in = (W - 1) * tm * 128
+    link_us = rows_in * k * 2 / (link_gbs * 1e3)
+    arrive = [start_us + (b + 1) / nbatch * link_us for b in range(nbatch)]
+    tile_us = 2.0 * 256 * 256 * k / (pair_tflops * 1e6)
+    units = []  # (ready, mt, nt, batch)
+    for rt2 in range(tm2):
+        for nt in range(tn):
+            units.append((0.0, rank * tm + 2 * rt2, nt, -1))
+    for rt2 in range(tm2):
+        b = min(nbatch - 1, (2 * rt2 + 1) * nbatch // tm)
+        for j in range(1, W):
+            src = (rank + j) % W
+            for nt in range(tn):
+                units.append((arrive[b], src * tm + 2 * rt2, nt, b))
+    units.sort(key=lambda u: u[0])  # stable: own rows, then batch by batch
+    n_last = sum(1 for u in units if u[3] == nbatch - 1)
+    split_from = len(units) - min(n_last, pairs) if (halves and W > 1) else len(units)
+    free = [(0.0, p) for p in range(pairs)]
+    heapq.heapify(free)
+    plan = [[] for _ in range(pairs)]
+    for idx, (ready, mt, nt, _) in enumerate(units):
+        parts = ((0, tile_us),) if idx < split_from else ((1, tile_us / 2 + 1.0), (2, tile_us / 2 + 1.0))
+        for half, dur in parts:
+            t, p = heapq.heappop(free)
+            plan[p].append((mt, nt, half))
+            heapq.heappush(free, (max(t, ready) + dur, p))
+    return plan
+
+
+def _ag_sched_tensor(w, r: int, tm: int, tn: int, pairs: int, nbatch: int, k: int, halves: bool, device):
+    cache = w.__dict__.setdefault("_ag_sched", {})
+    cfg = w.config
+    key = (r, tm, tn, pairs, nbatch, k, halves, cfg.ag_pair_tflops, cfg.ag_link_gbs)
+    t = cache.get(key)
+    if t is None:
+        plan = ag_pair_schedule(w.world_size, r, tm, tn, pairs, nbatch, k, halves=halves,
+                                pair_tflops=cfg.ag_pair_tflops, link_gbs=cfg.ag_link_gbs)
+        stride = max(len(x) for x in plan) + 1
+        rows = [[m | (n << 12) | (h << 28) for (m, n, h) in x] + [-1] * (stride - len(x)) for x in plan]
+        t = cache[key] = torch.tensor(rows, dtype=torch.int32).to(device)
+    return t
+
+
 def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, swiglu: bool = False, trace=None,
                     lsu_movers: bool = False, variant: str = "auto", world: Optional[WorldBase] = None):
     """``out_r = all_gather(a_shard) @ bt_r.T`` — tensor-parallel up-projection
@@ -228,6 +289,10 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.swiglu = 1 if swiglu else 0
         g.trace = _trace_ptr(w, trace, r, grid)
         g.lsu_movers = int(lsu_movers)  # pair kernel: 2 = move the shard only (timeline tool)
+        if pair and w.config.ag_schedule and W > 1:
+            nb = max(1, min(int(w.config.ag_batches), rows // 128))
+            sched = _ag_sched_tensor(w, r, rows // 128, -(-N // 256), grid // 2, nb, Kd, True, ar.device)
+            g.sched, g.sched_stride = sched.data_ptr(), sched.shape[1]
         arr[i] = g
     stream = torch.cuda.current_stream(a0.device).cuda_stream
     if pair:

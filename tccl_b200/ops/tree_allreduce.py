@@ -54,7 +54,9 @@ def _tree_grid(w: WorldBase, nbytes: int):
 
 def double_tree_all_reduce(tensor, out=None, *, inplace: bool = False, world: Optional[WorldBase] = None):
     w = get_world(world)
-    return _cached(w, _key("tree", w, tensor, out, inplace), lambda: _plan(w, tensor, out, inplace), tensor, out)
+    cfg = w.config  # the settings that shape the plan are part of its key
+    knobs = (cfg.tree_ll_max_bytes, cfg.tree_pull_min_bytes, cfg.tree_ctas, cfg.tree_chunk_bytes)
+    return _cached(w, _key("tree", w, tensor, out, inplace, knobs), lambda: _plan(w, tensor, out, inplace), tensor, out)
 
 
 def _plan(w: WorldBase, x, out, inplace: bool) -> Plan:

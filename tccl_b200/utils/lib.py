@@ -101,7 +101,7 @@ class AgGemmArgs(C.Structure):
         ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
         ("lda_shard", C.c_int32), ("lda_full", C.c_int32), ("ldb", C.c_int32), ("ldo", C.c_int32),
         ("comm_ctas", C.c_int32), ("swiglu", C.c_int32),
-        ("trace", C.c_uint64), ("lsu_movers", C.c_int32),
+        ("trace", C.c_uint64), ("lsu_movers", C.c_int32), ("sched_stride", C.c_int32), ("sched", C.c_uint64),
     ]
 
 

@@ -63,6 +63,34 @@ def test_all_gather_gemm(emu_worlds, W, M, N, K, variant):
             assert torch.equal(a_full[r].float(), a_all)  # the gathered activations are left behind, exactly
 
 
+@pytest.mark.parametrize("planned", [True, False])
+@pytest.mark.parametrize("batches", [1, 3, 4, 64])
+@pytest.mark.parametrize("W,M,N,K", [(2, 2048, 512, 256), (4, 2048, 264, 448)])
+def test_all_gather_gemm_pair_batch_counts(emu_worlds, W, M, N, K, batches, planned):
+    """The mover phase may send the shard in any number of batches (capped at one per row tile), and the
+    tiles may follow the host's plan (with half tiles at the end) or the kernel's built-in order."""
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    old = (w.config.ag_batches, w.config.ag_schedule)
+    w.config.ag_batches, w.config.ag_schedule = batches, planned
+    try:
+        shards = [_rand((M // W, K), 4100 + r) for r in range(W)]
+        bt = [_rand((N, K), 5100 + r, 0.02) for r in range(W)]
+        a_all = torch.cat(shards).float()
+        for rep in range(2):
+            outs, a_full = tccl.all_gather_gemm(shards, bt, variant="pair", world=w)
+            torch.cuda.synchronize()
+            w.check()
+            for r in range(W):
+                ref = a_all @ bt[r].float().t()
+                err = (outs[r].float() - ref).abs()
+                assert bool((err <= ref.abs() * 2 ** -8 + 1e-3 * (K ** 0.5) * 0.02).all())
+                assert torch.equal(a_full[r].float(), a_all)
+    finally:
+        w.config.ag_batches, w.config.ag_schedule = old
+
+
 @pytest.mark.parametrize("W", [1, 2, 4, 8])
 @pytest.mark.parametrize("T,H", [(8, 256), (67, 1024), (512, 4096), (33, 8192)])
 @pytest.mark.parametrize("with_res", [False, True])

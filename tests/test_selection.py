@@ -1,5 +1,6 @@
 """Host-side decision logic that needs no GPU: kernel choice by message size and world,
 grid sizing, tree chunking, weight packing."""
+import pytest
 import torch
 
 from tccl_b200.config import Config
@@ -113,3 +114,28 @@ def test_push_slot_is_fixed_per_world_not_per_message():
     w8, w3 = StubWorld(8, True), StubWorld(3, False)
     assert w8.push_max_bytes() == (2 << 20) // 16
     assert w3.push_max_bytes() % 16 == 0 and 2 * 3 * w3.push_max_bytes() <= w3.ll_bytes
+
+
+@pytest.mark.parametrize("W,tm,tn,pairs,nbatch", [(8, 4, 7, 74, 2), (8, 4, 7, 74, 4), (4, 8, 14, 74, 2), (2, 16, 28, 74, 2),
+                                                  (2, 2, 1, 4, 1), (3, 2, 3, 5, 2), (8, 2, 2, 74, 3)])
+def test_ag_pair_schedule_names_every_tile_once(W, tm, tn, pairs, nbatch):
+    """Whatever the cost model says, a plan must hold every tile exactly once: whole, or as its two halves."""
+    from tccl_b200.ops.fused import ag_pair_schedule
+
+    for rank in range(W):
+        for halves in (True, False):
+            plan = ag_pair_schedule(W, rank, tm, tn, pairs, nbatch, 512, halves=halves)
+            assert len(plan) == pairs
+            seen = {}
+            for units in plan:
+                for mt, nt, half in units:
+                    assert mt % 2 == 0 and 0 <= mt < W * tm and 0 <= nt < tn and half in (0, 1, 2)
+                    seen.setdefault((mt, nt), []).append(half)
+            assert len(seen) == W * (tm // 2) * tn
+            assert all(v == [0] or sorted(v) == [1, 2] for v in seen.values())
+            if not halves:
+                assert all(v == [0] for v in seen.values())
+            # the rank's own rows need no data from anybody: they come first wherever a pair has one
+            for units in plan:
+                own = [i for i, (mt, _, _) in enumerate(units) if mt // tm == rank]
+                assert own == list(range(len(own))) or W == 1
