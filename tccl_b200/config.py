@@ -45,10 +45,12 @@ class Config:
     tree_chunk_bytes: int = 16 << 20      # double-tree: most bytes per chunk (a chunk = one ring slice per CTA of a tree)
     tree_ctas: int = 36                   # double-tree: CTAs per (tree, direction); 4 x 36 = 144 of 148 SMs
     tree_ll_max_bytes: int = 2 << 20      # double-tree: up to here the flags travel inside the data lines
-    tree_pull_min_bytes: int = 0          # double-tree, chunked kernel: from here on children pull the sum from the parent
+    tree_pull_min_bytes: int = 1 << 62    # double-tree, chunked kernel: from here on children pull the sum from the parent
+                                          # (never by default: measured slower than pushing, 1921 vs 1765 us at 8 ranks, 512 MiB)
     ag_movers: int = 8                    # all-gather -> GEMM: CTAs that move the shard (two alternating groups);
                                           # measured on 8xB200: 8 -> 121 us, 16 -> 123, 24 -> 127, 32 -> 125
     ag_batches: int = 2                   # all-gather -> GEMM on CTA pairs: batches the shard goes out in (one fence each)
+    ag_ring: bool = False                 # ... movers send destination by destination (plain stores) instead of in batches to all
     ag_schedule: bool = True              # ... its tiles follow a host-made plan (list scheduling against the rows' arrival)
     ag_pair_tflops: float = 20.0          # ... cost model of that plan: bf16 TFLOP/s of one CTA pair,
     ag_link_gbs: float = 600.0            # ... and GB/s at which the peers' rows arrive

@@ -42,6 +42,7 @@ struct alignas(64) AgGemmPairParams {
   const int32_t* sched;  // optional: every pair's tiles in running order (see tccl_ag_gemm_args)
   int sched_stride;
   int batches;      // batches the shard's row tiles go out in (each ends in one system-scope fence)
+  int ring;         // movers send destination by destination (plain stores) instead of batch by batch to all
   int movers_only;  // diagnostic (timeline tool): move the shard, compute nothing
   uint64_t* trace;  // optional: 64 words per CTA of %globaltimer stamps (see run_mainloop2); [61] kernel end
 };
@@ -76,8 +77,17 @@ struct AgGemmPairPolicy {
       nt = t % tn;
       return true;
     }
-    // remote rows in arrival order: pair-row by pair-row, peers from the next rank on
     const int u = t - own;
+    if (p->ring) {
+      // rows arrive source by source, the previous rank's first (it sends to its next rank first)
+      const int j = u / own, v = u - j * own;
+      int src = c->rank - 1 - j;
+      if (src < 0) src += W;
+      mt = src * p->tiles_m_per_rank + 2 * (v / tn);
+      nt = v % tn;
+      return true;
+    }
+    // batches to all ranks at once: pair-row by pair-row, peers from the next rank on
     const int per_rt = (W - 1) * tn;
     const int rt2 = u / per_rt, v = u - rt2 * per_rt;
     int src = c->rank + 1 + v / tn;
@@ -94,6 +104,62 @@ struct AgGemmPairPolicy {
   __device__ __forceinline__ void epilogue_finish(int, int, const Abort&) const {}
   __device__ __forceinline__ void between_tiles(int, int, const Abort&) const {}
 
+  // Ring-ordered form of the data-mover phase: W - 1 rounds, in round j every CTA stores its share of
+  // the WHOLE shard into the gathered buffer of rank (me + j) only, with plain stores.  Every round is
+  // a permutation (each GPU sends to one peer and receives from one), so a receiver has the previous
+  // rank's rows after one round at full link rate, the rows of the rank before that after two, ... —
+  // its pairs start on remote tiles after 1 / (W - 1) of the transfer instead of after half of it,
+  // and W - 1 copies on the wire cost no more inbound bytes than the switch's multicast (which also
+  // returns every row to its sender).  One system-scope fence per round; the CTA that completes a
+  // round raises the flags of all the shard's row tiles at that round's destination.  The own rows go
+  // into the own gathered buffer last (nobody waits for them: the GEMM reads them from the shard).
+  __device__ void ring_movers(int t, uint32_t lo, uint32_t hi, int vec_per_row, int rows_per_rank, uint64_t hoff,
+                              int nb) const {
+    const int W = c->world, me = c->rank, tm = p->tiles_m_per_rank;
+    constexpr int U = 8;
+    for (int j = 1; j <= W; ++j) {
+      const int dst = (me + j) % W;  // j == W: the own buffer
+      char* base = p->a_full[dst] + hoff;
+      for (int rt = 0; rt < tm; ++rt) {
+        for (uint32_t i0 = lo + t; i0 < hi; i0 += U * 128) {
+          Vec16 v[U];
+          size_t off[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * 128;
+            if (i < hi) {
+              const int row = rt * 128 + i / vec_per_row, col = (i % vec_per_row) * 8;
+              v[u] = ld_peer(p->a_shard + ((size_t)row * p->lda_shard + col) * 2);
+              off[u] = ((size_t)(me * rows_per_rank + row) * p->lda_full + col) * 2;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * 128 < hi) st_peer(base + off[u], v[u]);
+        }
+      }
+      if (j == W) break;  // local copy: no flags
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // this CTA's share of the round is stored
+      if (t == 0) {
+        if (trace && j <= 2) trace[62 - 2 * j] = globaltimer();
+        fence_acq_rel_sys();
+        if (trace && j <= 2) trace[61 - 2 * j] = globaltimer();
+        const uint32_t done = atomicAdd(c->local + TCCL_LOCAL_AGCNT + (j - 1), 1u);
+        *s_last = (done == (uint32_t)nb - 1u);
+        if (*s_last) {
+          c->local[TCCL_LOCAL_AGCNT + (j - 1)] = 0u;
+          fence_acq_rel_sys();
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*reinterpret_cast<volatile int*>(s_last)) {
+        for (int k = t; k < tm; k += 128)
+          st_release_sys(c->flags[dst] + TCCL_FLAG_AG + me * TCCL_MAX_ROW_TILES + k, epoch);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // s_last is rewritten by the next round
+    }
+  }
+
   // The data-mover phase, run by the four epilogue warps of EVERY CTA while the producer and MMA
   // warps already work on the rank's own rows (the first accumulator is tens of microseconds
   // away).  The shard's row tiles go out in `batches` batches; in each, CTA b stores its 1/grid share of
@@ -109,6 +175,10 @@ struct AgGemmPairPolicy {
     const uint32_t nvec = 128u * (uint32_t)vec_per_row;
     const uint32_t per = (nvec + nb - 1) / nb;
     const uint32_t lo = min(per * (uint32_t)bid, nvec), hi = min(lo + per, nvec);
+    if (p->ring) {
+      ring_movers(t, lo, hi, vec_per_row, rows_per_rank, hoff, nb);
+      return;
+    }
     const int nbatch = max(1, min(p->batches, p->tiles_m_per_rank));
     for (int b = 0; b < nbatch; ++b) {
       const int rt0 = b * p->tiles_m_per_rank / nbatch, rt1 = (b + 1) * p->tiles_m_per_rank / nbatch;
@@ -308,7 +378,8 @@ static int fill_params(AgGemmPairParams* p, const tccl_ag_gemm_args* g, int worl
   p->tiles_m_per_rank = rows / 128;
   p->swiglu = g->swiglu;
   p->batches = g->comm_ctas > 0 ? g->comm_ctas : 2;
-  p->movers_only = g->lsu_movers == 2;
+  p->movers_only = (g->lsu_movers & 2) != 0;
+  p->ring = (g->lsu_movers & 4) != 0;
   p->trace = reinterpret_cast<uint64_t*>(g->trace);
   if (g->swiglu && (g->n % BN2)) return -TCCL_ESIZE;  // whole gate|up tiles only
   if (p->tiles_m_per_rank > TCCL_MAX_ROW_TILES) return -TCCL_ESIZE;
@@ -324,8 +395,8 @@ using namespace tccl::gemm2;
 extern "C" uint64_t tccl_ag_gemm_pair_param_bytes(void) { return sizeof(AgGemmPairParams); }
 
 // Same calling convention as tccl_allgather_gemm, except that every CTA moves data first: comm_ctas of
-// the arguments is the number of batches the shard goes out in (0 = 2), lsu_movers == 2 the diagnostic
-// "move only".  `half_bytes`: distance in bytes from a_full[q] to the second
+// the arguments is the number of batches the shard goes out in (0 = 2); lsu_movers is a set of bits:
+// 2 = the diagnostic "move only", 4 = ring-ordered movers (ring_movers above).  `half_bytes`: distance in bytes from a_full[q] to the second
 // half of every rank's gathered buffer, or 0 when there is only one buffer (then the kernel opens
 // with a barrier).  l->grid must be even.
 extern "C" int tccl_allgather_gemm_pair(const tccl_comm* comm, const tccl_ag_gemm_args* args, void* dev_params,

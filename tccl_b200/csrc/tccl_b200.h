@@ -200,8 +200,8 @@ typedef struct tccl_tree_args {
   int32_t child_slot[2];     /* 0 if this rank is its parent's left child, 1 if right */
 } tccl_tree_args;
 /* TCCL_TREE_PULL_DOWN in l->meta: on the way down the children load the sum from their parent's result
- * buffer instead of the parent storing it into theirs — the form for large messages (buf must then be
- * readable by the children until they have acknowledged, which the kernel waits for) */
+ * buffer instead of the parent storing it into theirs (buf must then be readable by the children until they
+ * have acknowledged, which the kernel waits for); measured slower than pushing, so off by default */
 #define TCCL_TREE_PULL_DOWN 256
 int tccl_allreduce_tree(const tccl_comm*, const tccl_tree_args*, const tccl_launch*);
 /* CTAs per role that a ring of `tree_bytes` can serve (<= TCCL_TREE_MAX_CTAS) */
@@ -314,7 +314,8 @@ int tccl_allgather_gemm(const tccl_comm* comm, const tccl_ag_gemm_args* args, vo
                         const tccl_launch* l);
 
 /* Same product on CTA pairs (tcgen05.mma.cta_group::2); every CTA moves its share of the shard first
- * (comm_ctas = batches of that phase, 0 = 2; lsu_movers == 2 = move only).  m % (world * 256) == 0; l->grid even.  `half_bytes`: distance
+ * (comm_ctas = batches of that phase, 0 = 2; lsu_movers bit 2 = move only, bit 4 = send destination by
+ * destination with plain stores instead of batch by batch to all ranks).  m % (world * 256) == 0; l->grid even.  `half_bytes`: distance
  * from a_full[q] to the second half of every rank's gathered buffer — the halves alternate from call to
  * call and no entry barrier is needed — or 0 for a single buffer (the kernel then opens with a barrier). */
 uint64_t tccl_ag_gemm_pair_param_bytes(void);

@@ -33,17 +33,23 @@
 // its owner only; and a result buffer is written by the parent only after the
 // owner has contributed the same chunk of the same call.
 //
-// Two forms of the way down.  Push (`kPullDown` false): a parent stores the sum
-// into its children's result buffers, as described above: one crossing per
-// level, the form for latency.  Pull (`kPullDown` true): a parent only bumps its
+// Two forms of the way down.  Push (`kPullDown` false, the default): a parent
+// stores the sum into its children's result buffers, as described above: one
+// crossing per level.  Pull (`kPullDown` true): a parent only bumps its
 // children's DOWN counter and each child LOADS the slice from the parent's
-// result buffer.  An SM sustains only a few GB/s of peer traffic, and a pushing
-// parent has two children to serve with the same CTAs; pulling spreads the down
-// traffic over the children's SMs, which is what large messages need.  A parent
-// whose buffer is pulled from must not return while a child may still be
-// reading (its caller may overwrite the buffer next): each child acknowledges
-// every slice it has pulled (DACK counter at the parent) and the parent's down
-// worker waits for the last acknowledgement before it leaves.
+// result buffer, which moves the down traffic's issue from the parent's SMs
+// (two children to serve) to the children's.  A parent whose buffer is pulled
+// from must not return while a child may still be reading (its caller may
+// overwrite the buffer next): each child acknowledges every slice it has pulled
+// (DACK counter at the parent) and the parent's down worker waits for the last
+// acknowledgement before it leaves.  Measured, pushing wins (512 MiB: 859 vs
+// 963 us at 2 ranks, 1765 vs 1921 us at 8): the link is what both forms fill, and
+// the pull adds a load round trip per slice.
+//
+// What a slice costs is protocol, not data: a flag crossing, and a release that
+// waits until every store of the CTA has been acknowledged.  Hence large ring
+// slices (TCCL_TREE_SLICE_BYTES) and ONE fence.acq_rel.sys per slice followed by
+// relaxed stores of all the counters, instead of a st.release per counter.
 //
 // The element count must be a whole number of 16-byte vectors (the reference
 // asks the same: triton_double_tree_allreduce.py:346-348).
@@ -250,7 +256,7 @@ extern "C" int tccl_allreduce_tree(const tccl_comm* comm, const tccl_tree_args* 
     if (K < 1 || K > tree_max_ctas(comm->tree_bytes) || l->grid != 4 * K) return -TCCL_ESIZE;
     if (args->chunk_vecs < 1 || args->chunk_vecs > (uint64_t)K * (TCCL_TREE_SLICE_BYTES / 16)) return -TCCL_ESIZE;
   }
-  if (l->meta & TCCL_TREE_PULL_DOWN) {  // large messages: children load the sum from their parent
+  if (l->meta & TCCL_TREE_PULL_DOWN) {  // on request: children load the sum from their parent
     switch (dtype) {
       case TCCL_BF16: return launch_op<TreeAllReduce<__nv_bfloat16, true>>(comm, args, l);
       case TCCL_F32: return launch_op<TreeAllReduce<float, true>>(comm, args, l);

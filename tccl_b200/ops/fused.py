@@ -131,15 +131,17 @@ def gemm_reduce_scatter(a, bt, out=None, *, trace=None, variant: str = "auto", w
 
 
 def ag_pair_schedule(W: int, rank: int, tm: int, tn: int, pairs: int, nbatch: int, k: int, *, halves: bool = True,
-                     pair_tflops: float = 20.0, link_gbs: float = 600.0, start_us: float = 8.0):
+                     ring: bool = False, pair_tflops: float = 20.0, link_gbs: float = 600.0, start_us: float = 8.0,
+                     round_us: float = 2.0):
     """Plan of the all-gather -> GEMM pair kernel: for every CTA pair the tiles it runs, in order.
 
     The kernel's built-in order deals tile ``pair + i * pairs`` to a pair whatever the moment its rows
     arrive; at 8 ranks most pairs then sit on a remote tile while others queue two tiles behind theirs.
     This is list scheduling against a small cost model instead: the rank's own rows are there at once,
     batch ``b`` of the peers' rows (``nbatch`` batches of ``tm / nbatch`` 128-row tiles per rank) after
-    ``start_us + (b + 1) / nbatch`` of the time the link needs for all of them, a 256 x 256 tile costs
-    ``2 * 256 * 256 * k / pair_tflops``.  Tiles are taken in the order their rows arrive and handed to
+    ``start_us + (b + 1) / nbatch`` of the time the link needs for all of them (``ring``: the movers send
+    destination by destination, so the rows of rank ``rank - j`` are there after ``j`` rounds of one shard
+    each plus ``round_us`` per round), a 256 x 256 tile costs ``2 * 256 * 256 * k / pair_tflops``.  Tiles are taken in the order their rows arrive and handed to
     the pair that is free first; the last tiles (those of the last batch, one wave at most) are cut into
     256 x 128 halves so that the work left when the last rows land spreads over all pairs.  Returns
     ``pairs`` lists of ``(mt, nt, half)`` (``mt`` = even 128-row tile index, ``half`` 0 / 1 / 2 = whole
@@ -152,18 +154,28 @@ def ag_pair_schedule(W: int, rank: int, tm: int, tn: int, pairs: int, nbatch: in
     link_us = rows_in * k * 2 / (link_gbs * 1e3)
     arrive = [start_us + (b + 1) / nbatch * link_us for b in range(nbatch)]
     tile_us = 2.0 * 256 * 256 * k / (pair_tflops * 1e6)
-    units = []  # (ready, mt, nt, batch)
+    units = []  # (ready, mt, nt, group): group = batch (or round) the rows come with, -1 = own
     for rt2 in range(tm2):
         for nt in range(tn):
             units.append((0.0, rank * tm + 2 * rt2, nt, -1))
-    for rt2 in range(tm2):
-        b = min(nbatch - 1, (2 * rt2 + 1) * nbatch // tm)
+    last = nbatch - 1
+    if ring:
+        shard_us = tm * 128 * k * 2 / (link_gbs * 1e3)
+        last = W - 1
         for j in range(1, W):
-            src = (rank + j) % W
-            for nt in range(tn):
-                units.append((arrive[b], src * tm + 2 * rt2, nt, b))
+            src = (rank - j) % W
+            for rt2 in range(tm2):
+                for nt in range(tn):
+                    units.append((start_us + j * (shard_us + round_us), src * tm + 2 * rt2, nt, j))
+    else:
+        for rt2 in range(tm2):
+            b = min(nbatch - 1, (2 * rt2 + 1) * nbatch // tm)
+            for j in range(1, W):
+                src = (rank + j) % W
+                for nt in range(tn):
+                    units.append((arrive[b], src * tm + 2 * rt2, nt, b))
     units.sort(key=lambda u: u[0])  # stable: own rows, then batch by batch
-    n_last = sum(1 for u in units if u[3] == nbatch - 1)
+    n_last = sum(1 for u in units if u[3] == last)
     split_from = len(units) - min(n_last, pairs) if (halves and W > 1) else len(units)
     free = [(0.0, p) for p in range(pairs)]
     heapq.heapify(free)
@@ -180,10 +192,10 @@ def ag_pair_schedule(W: int, rank: int, tm: int, tn: int, pairs: int, nbatch: in
 def _ag_sched_tensor(w, r: int, tm: int, tn: int, pairs: int, nbatch: int, k: int, halves: bool, device):
     cache = w.__dict__.setdefault("_ag_sched", {})
     cfg = w.config
-    key = (r, tm, tn, pairs, nbatch, k, halves, cfg.ag_pair_tflops, cfg.ag_link_gbs)
+    key = (r, tm, tn, pairs, nbatch, k, halves, bool(cfg.ag_ring), cfg.ag_pair_tflops, cfg.ag_link_gbs)
     t = cache.get(key)
     if t is None:
-        plan = ag_pair_schedule(w.world_size, r, tm, tn, pairs, nbatch, k, halves=halves,
+        plan = ag_pair_schedule(w.world_size, r, tm, tn, pairs, nbatch, k, halves=halves, ring=bool(cfg.ag_ring),
                                 pair_tflops=cfg.ag_pair_tflops, link_gbs=cfg.ag_link_gbs)
         stride = max(len(x) for x in plan) + 1
         rows = [[m | (n << 12) | (h << 28) for (m, n, h) in x] + [-1] * (stride - len(x)) for x in plan]
@@ -255,7 +267,7 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
                 ret_full = EmuTensor([t[seq & 1] for t in a_full.parts])
     full_ptrs = w.peer_ptrs(a_full)
     # two ranks: the switch would deliver every row to its sender too (twice the inbound bytes of a plain store)
-    mc = w.mc_ptr(a_full) if (W > 2 or not pair) else 0
+    mc = w.mc_ptr(a_full) if ((W > 2 and not w.config.ag_ring) or not pair) else 0
     lib = L.lib()
     lib.tccl_ag_gemm_param_bytes.restype = C.c_uint64
     lib.tccl_ag_gemm_pair_param_bytes.restype = C.c_uint64
@@ -288,7 +300,9 @@ def all_gather_gemm(a_shard, bt, a_full=None, out=None, *, comm_ctas: int = 0, s
         g.comm_ctas = max(1, int(w.config.ag_batches)) if pair else comm_ctas  # pair kernel: batches of the mover phase
         g.swiglu = 1 if swiglu else 0
         g.trace = _trace_ptr(w, trace, r, grid)
-        g.lsu_movers = int(lsu_movers)  # pair kernel: 2 = move the shard only (timeline tool)
+        g.lsu_movers = int(lsu_movers)
+        if pair:  # bits: 2 = move the shard only (timeline tool), 4 = movers send destination by destination
+            g.lsu_movers = (2 if int(lsu_movers) == 2 else 0) | (4 if w.config.ag_ring else 0)
         if pair and w.config.ag_schedule and W > 1:
             nb = max(1, min(int(w.config.ag_batches), rows // 128))
             sched = _ag_sched_tensor(w, r, rows // 128, -(-N // 256), grid // 2, nb, Kd, True, ar.device)

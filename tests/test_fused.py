@@ -64,16 +64,17 @@ def test_all_gather_gemm(emu_worlds, W, M, N, K, variant):
 
 
 @pytest.mark.parametrize("planned", [True, False])
-@pytest.mark.parametrize("batches", [1, 3, 4, 64])
-@pytest.mark.parametrize("W,M,N,K", [(2, 2048, 512, 256), (4, 2048, 264, 448)])
+@pytest.mark.parametrize("batches", [0, 1, 3, 4, 64])
+@pytest.mark.parametrize("W,M,N,K", [(2, 2048, 512, 256), (4, 2048, 264, 448), (8, 4096, 256, 128)])
 def test_all_gather_gemm_pair_batch_counts(emu_worlds, W, M, N, K, batches, planned):
     """The mover phase may send the shard in any number of batches (capped at one per row tile), and the
     tiles may follow the host's plan (with half tiles at the end) or the kernel's built-in order."""
     import tccl_b200 as tccl
 
     w = emu_worlds(W)
-    old = (w.config.ag_batches, w.config.ag_schedule)
-    w.config.ag_batches, w.config.ag_schedule = batches, planned
+    old = (w.config.ag_batches, w.config.ag_schedule, w.config.ag_ring)
+    # batches == 0: the ring-ordered movers (destination by destination); else batches to all ranks at once
+    w.config.ag_batches, w.config.ag_schedule, w.config.ag_ring = max(1, batches), planned, batches == 0
     try:
         shards = [_rand((M // W, K), 4100 + r) for r in range(W)]
         bt = [_rand((N, K), 5100 + r, 0.02) for r in range(W)]
@@ -88,7 +89,7 @@ def test_all_gather_gemm_pair_batch_counts(emu_worlds, W, M, N, K, batches, plan
                 assert bool((err <= ref.abs() * 2 ** -8 + 1e-3 * (K ** 0.5) * 0.02).all())
                 assert torch.equal(a_full[r].float(), a_all)
     finally:
-        w.config.ag_batches, w.config.ag_schedule = old
+        w.config.ag_batches, w.config.ag_schedule, w.config.ag_ring = old
 
 
 @pytest.mark.parametrize("W", [1, 2, 4, 8])

@@ -123,8 +123,8 @@ def test_ag_pair_schedule_names_every_tile_once(W, tm, tn, pairs, nbatch):
     from tccl_b200.ops.fused import ag_pair_schedule
 
     for rank in range(W):
-        for halves in (True, False):
-            plan = ag_pair_schedule(W, rank, tm, tn, pairs, nbatch, 512, halves=halves)
+        for halves, ring in ((True, False), (False, False), (True, True), (False, True)):
+            plan = ag_pair_schedule(W, rank, tm, tn, pairs, nbatch, 512, halves=halves, ring=ring)
             assert len(plan) == pairs
             seen = {}
             for units in plan:
