@@ -16,7 +16,8 @@ from ..parallel.world import WorldBase
 from ..utils import lib as L
 from ._common import K, check_sym_tensor, dtype_code, get_world
 
-__all__ = ["gemm_reduce_scatter", "all_gather_gemm", "all_reduce_bias_residual_rmsnorm", "pack_gate_up"]
+__all__ = ["gemm_reduce_scatter", "all_gather_gemm", "all_reduce_bias_residual_rmsnorm", "pack_gate_up",
+           "ag_pair_schedule"]
 
 
 def _locals(w: WorldBase, x):
