@@ -257,6 +257,8 @@ def main():
                     if w.has_nvls:
                         algos += (["oneshot_nvls"] if S <= (8 << 20) else []) + ["twoshot_nvls"]
                         algos += ["push_nvls"] if push_ok else []
+                    if W == 2 and S >= (16 << 20):
+                        algos += ["twoshot_bulk_p2p"]
                     if S >= (1 << 20):
                         algos += ["twoshot_pipe_nvls" if w.has_nvls and W > 2 else "twoshot_pipe_p2p"]
                     algos += ["tree"] if S >= 4096 else []

@@ -40,6 +40,7 @@ class Config:
     nvls_twoshot_min_bytes: int = 16 * 1024   # all-reduce with a switch and a symmetric destination: two-shot NVLS above this
     push_max_bytes: int = 64 * 1024       # all-reduce: push variant (one barrier, local sum) up to here
     oneshot_max_bytes: int = 512 * 1024   # all-reduce: one-shot up to here, two-shot above
+    bulk_min_bytes: int = 64 << 20        # all-reduce at two ranks: from here on the two-shot that moves data with bulk copies (0 = never)
     staged_twoshot: bool = True           # large all-reduce into ordinary memory: two-shot via a cached symmetric buffer
     staged_max_bytes: int = 1 << 30       # ... up to this message size (the buffer is kept per size and dtype)
     tree_chunk_bytes: int = 16 << 20      # double-tree: most bytes per chunk (a chunk = one ring slice per CTA of a tree)

@@ -179,6 +179,10 @@ int tccl_allreduce_twoshot_nvls(const tccl_comm*, const tccl_coll_args*, const t
 /* two-shot with reducer and broadcaster warps decoupled through a shared-memory ring (block = 512) */
 int tccl_allreduce_twoshot_pipe_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allreduce_twoshot_pipe_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
+/* Two-shot all-reduce that moves the data with bulk async copies (global -> shared -> global; no thread touches
+ * remote memory).  l->block must be 256; dynamic shared memory is (3 * world + 2) * tccl_allreduce_bulk_chunk_bytes(). */
+uint32_t tccl_allreduce_bulk_chunk_bytes(int world);
+int tccl_allreduce_twoshot_bulk(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_pull_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_push_p2p(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);
 int tccl_allgather_push_nvls(const tccl_comm*, const tccl_coll_args*, const tccl_launch*);

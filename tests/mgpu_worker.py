@@ -61,7 +61,7 @@ def main():
             traceback.print_exc()
 
     nvls = w.has_nvls
-    ar_algos = ["oneshot_p2p", "twoshot_p2p", "twoshot_pipe_p2p"] + (
+    ar_algos = ["oneshot_p2p", "twoshot_p2p", "twoshot_pipe_p2p", "twoshot_bulk_p2p"] + (
         ["oneshot_nvls", "twoshot_nvls", "twoshot_pipe_nvls"] if nvls else [])
     push_algos = ["push_p2p"] + (["push_nvls"] if nvls else [])
 

@@ -139,6 +139,37 @@ def test_all_reduce_twoshot_pipelined(emu_worlds, W, dtype, shape, n):
         w.config.pipe_reducers, w.config.pipe_stages, w.config.pipe_unroll = old
 
 
+@pytest.mark.parametrize("W", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [8, 1000, 65536 + 24, 3 * (1 << 20) + 5, 12 * (1 << 20)])
+def test_all_reduce_twoshot_bulk_copies(emu_worlds, W, dtype, n):
+    """The two-shot kernel that moves its data with bulk async copies (loader / reducers / storer around
+    shared-memory stages): in place twice in a row, then into a separate symmetric tensor."""
+    import tccl_b200 as tccl
+
+    w = emu_worlds(W)
+    for seed in (2000, 2100):
+        x = make_inputs(w, W, n, dtype, seed)
+        ref = ref_sum(x)
+        res = tccl.all_reduce(x, inplace=True, algo="twoshot_bulk_p2p", world=w)
+        torch.cuda.synchronize()
+        w.check()
+        assert res is x
+        for r in range(W):
+            assert_close_to_sum(x[r], ref, dtype, W)
+            assert torch.equal(x[r], x[0])
+    x = make_inputs(w, W, n, dtype, 2200)
+    keep = [p.clone() for p in x.parts]
+    ref = ref_sum(x)
+    out = w.empty(n, dtype)
+    tccl.all_reduce(x, out=out, algo="twoshot_bulk_p2p", world=w)
+    torch.cuda.synchronize()
+    w.check()
+    for r in range(W):
+        assert torch.equal(x[r], keep[r])
+        assert_close_to_sum(out[r], ref, dtype, W)
+
+
 def test_all_reduce_twoshot_symmetric_out_keeps_input(emu_worlds):
     import tccl_b200 as tccl
 

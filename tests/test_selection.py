@@ -46,7 +46,8 @@ def test_all_reduce_choice_follows_size_and_world():
     assert choose_all_reduce_algo(w8, 4100, True) == "oneshot_nvls"           # not a multiple of 16 bytes: no push
     w2 = StubWorld(2, True)  # two ranks: NVLS moves more bytes than P2P
     assert choose_all_reduce_algo(w2, 4096, True) == "push_p2p"
-    assert choose_all_reduce_algo(w2, 64 << 20, True) == "twoshot_p2p"
+    assert choose_all_reduce_algo(w2, 32 << 20, True) == "twoshot_p2p"
+    assert choose_all_reduce_algo(w2, 64 << 20, True) == "twoshot_bulk_p2p"  # two ranks, large: bulk copies
     w4 = StubWorld(4, False)
     assert choose_all_reduce_algo(w4, 64 << 20, True) == "twoshot_p2p"
     assert choose_all_reduce_algo(StubWorld(1, False), 1 << 30, True) == "oneshot_p2p"
