@@ -15,7 +15,12 @@ buffer*, which therefore lives in symmetric memory: ``tensor`` itself with
 which the kernel copies each slice into an ordinary output tensor (a fresh one
 per call unless ``out=`` is given), so ``tensor`` stays intact like the
 reference's wrapper and two results never alias.  Only the in-place form needs
-``tensor`` in symmetric memory.
+``tensor`` in symmetric memory.  (``tree_pull_min_bytes`` switches the way down
+to the other form: children load the sum from the parent's result buffer.)
+
+Messages up to ``tree_ll_max_bytes`` (2 MiB) take a kernel of their own whose
+16-byte lines carry the call number next to the data (``tree_allreduce_ll.cu``):
+no counters, no fences, and nothing has to be symmetric, in place or not.
 """
 from __future__ import annotations
 
@@ -37,7 +42,7 @@ _LL_SLOT = K["TCCL_TREE_LL_SLOT_BYTES"]
 
 def _tree_grid(w: WorldBase, nbytes: int):
     """(K, chunk_vecs): CTAs per role and 16-byte vectors per chunk.  A CTA moves at most one
-    ring slice (64 KiB) of a chunk; small messages use few CTAs (latency), large ones all the
+    ring slice (``TCCL_TREE_SLICE_BYTES``, 256 KiB) of a chunk; small messages use few CTAs (latency), large ones all the
     ring serves, with at least four chunks per tree so that the up and down phases overlap."""
     cfg = w.config
     kmax = max(1, min(cfg.tree_ctas, K["TCCL_TREE_MAX_CTAS"], max(1, w.max_ctas() // 4)))
