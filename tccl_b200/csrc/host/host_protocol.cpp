@@ -615,3 +615,183 @@ extern "C" int hp_selftest_push(int world, int calls, int scheme) {
   for (auto& x : th) x.join();
   return bad.load();
 }
+
+// ---------------------------------------------------------------------------
+// Model of the bulk-copy two-shot all-reduce (allreduce_bulk.cu).  Per rank and CTA: a loader, a
+// few reducers and a storer around 3 input stages and 2 output stages guarded by mbarriers
+// (modelled with an arrival count and a phase), and a COPY ENGINE thread that runs the bulk
+// copies later than they are issued — a load arrives on the stage's barrier when its bytes have
+// landed, a store group counts as "read" only once the engine has copied it — so a stage that is
+// released or refilled too early shows up as a data race.  Ranks meet at the epoch barrier on
+// entry and on exit; two calls run back to back, in place.
+namespace {
+struct Mbar {
+  std::atomic<int> pending{0};
+  std::atomic<uint32_t> phase{0};
+  int count = 0;
+  void init(int n) {
+    count = n;
+    pending.store(n, std::memory_order_relaxed);
+    phase.store(0, std::memory_order_relaxed);
+  }
+  void arrive() {
+    if (pending.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+      pending.store(count, std::memory_order_relaxed);
+      phase.fetch_add(1, std::memory_order_release);
+    }
+  }
+  // like mbarrier.try_wait.parity in a loop: returns once the phase with this parity has completed
+  void wait(uint32_t parity) const {
+    while ((phase.load(std::memory_order_acquire) & 1u) == parity) std::this_thread::yield();
+  }
+};
+struct CopyJob {
+  float* dst;
+  const float* src;
+  size_t n;
+  Mbar* arrive_on;  // loads: the stage's "full" barrier; stores: null
+  int group;        // stores: bulk group number (-1 for loads)
+};
+struct CopyEngine {
+  std::vector<CopyJob> jobs;             // written by the issuing threads under `lock`, read by the engine
+  std::atomic<int> issued{0}, taken{0};
+  std::atomic<int> groups_read{0};       // store groups whose source stage has been read
+  std::atomic<bool> stop{false};
+  std::atomic_flag lock = ATOMIC_FLAG_INIT;
+  explicit CopyEngine(size_t cap) : jobs(cap) {}
+  void submit(const CopyJob& j) {
+    while (lock.test_and_set(std::memory_order_acquire)) std::this_thread::yield();
+    jobs[(size_t)issued.load(std::memory_order_relaxed)] = j;
+    issued.fetch_add(1, std::memory_order_release);
+    lock.clear(std::memory_order_release);
+  }
+  void run() {
+    for (;;) {
+      const int t = taken.load(std::memory_order_relaxed);
+      if (t < issued.load(std::memory_order_acquire)) {
+        const CopyJob j = jobs[(size_t)t];
+        std::memcpy(j.dst, j.src, j.n * sizeof(float));
+        if (j.arrive_on) j.arrive_on->arrive();
+        if (j.group >= 0) groups_read.store(j.group + 1, std::memory_order_release);
+        taken.store(t + 1, std::memory_order_release);
+      } else if (stop.load(std::memory_order_acquire)) {
+        return;
+      } else {
+        std::this_thread::yield();
+      }
+    }
+  }
+};
+}  // namespace
+
+// `early_release` != 0 is the mistake the output stages guard against, kept so that the sanitizer can be seen to
+// catch it: the storer frees a stage as soon as its copies are ISSUED instead of when they have read it.
+extern "C" int hp_selftest_bulk(int world, int ctas, int chunk, int chunks_per_cta, int calls, int early_release) {
+  if (world < 1 || world > TCCL_MAX_WORLD || ctas < 1 || ctas > 8) return 100;
+  constexpr int kIn = 3, kOut = 2, kReducers = 3;
+  const size_t per = (size_t)ctas * chunks_per_cta * chunk - (size_t)chunk / 3;  // a ragged last chunk
+  const size_t numel = per * world;
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> data(world, std::vector<float>(numel));
+  std::atomic<int> bad{0};
+  std::vector<KernelBoundary> boundary(world);
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    for (int bid = 0; bid < ctas; ++bid)
+      th.emplace_back([&, r, bid] {
+        // one "CTA": its shared memory, barriers and copy engine live here; its roles are threads
+        HostComm c;
+        c.world = world;
+        c.rank = r;
+        for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+        c.local = local[r].data();
+        c.timeout_ns = 60ull * 1000 * 1000 * 1000;
+        Faults none{-1, 0, -1};
+        std::vector<float> in_st((size_t)kIn * world * chunk), out_st((size_t)kOut * chunk);
+        int my_sense = 0;
+        for (int call = 0; call < calls; ++call) {
+          if (bid == 0)  // the "host" of rank r fills its input between two kernels
+            for (size_t i = 0; i < numel; ++i) data[r][i] = (float)((r + 1) * (int)(i % 5 + 1) + call);
+          boundary[r].arrive_and_wait(ctas, my_sense);
+          const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+          Mbar full_in[kIn], empty_in[kIn], full_out[kOut], empty_out[kOut];
+          for (int s = 0; s < kIn; ++s) {
+            full_in[s].init(world);  // one arrival per landed copy (the kernel counts bytes instead)
+            empty_in[s].init(kReducers);
+          }
+          for (int s = 0; s < kOut; ++s) {
+            full_out[s].init(kReducers);
+            empty_out[s].init(1);
+          }
+          if (!barrier(c, bid, deadline, none)) bad.store(1);  // entry: every rank's input is written
+          const size_t lo = per * r;
+          const size_t nchunks = (per + chunk - 1) / chunk;
+          CopyEngine eng((size_t)(2 * world) * (nchunks / ctas + 2));
+          std::thread engine([&] { eng.run(); });
+          std::thread loader([&] {
+            uint32_t q = 0;
+            for (size_t ci = bid; ci < nchunks; ci += ctas, ++q) {
+              const int s = q % kIn;
+              empty_in[s].wait(((q / kIn) & 1u) ^ 1u);
+              const size_t v0 = lo + ci * chunk, cnt = std::min((size_t)chunk, lo + per - v0);
+              for (int p = 0; p < world; ++p)
+                eng.submit({in_st.data() + ((size_t)s * world + p) * chunk, data[p].data() + v0, cnt, &full_in[s], -1});
+            }
+          });
+          std::vector<std::thread> reducers;
+          for (int j = 0; j < kReducers; ++j)
+            reducers.emplace_back([&, j] {
+              uint32_t q = 0;
+              for (size_t ci = bid; ci < nchunks; ci += ctas, ++q) {
+                const int s = q % kIn, so = q % kOut;
+                full_in[s].wait((q / kIn) & 1u);
+                empty_out[so].wait(((q / kOut) & 1u) ^ 1u);
+                const size_t v0 = lo + ci * chunk, cnt = std::min((size_t)chunk, lo + per - v0);
+                for (size_t k = j; k < cnt; k += kReducers) {
+                  float sum = 0.f;
+                  for (int p = 0; p < world; ++p) sum += in_st[((size_t)s * world + p) * chunk + k];
+                  out_st[(size_t)so * chunk + k] = sum;
+                }
+                full_out[so].arrive();
+                empty_in[s].arrive();
+              }
+            });
+          std::thread storer([&] {
+            uint32_t q = 0;
+            for (size_t ci = bid; ci < nchunks; ci += ctas, ++q) {
+              const int so = q % kOut;
+              full_out[so].wait((q / kOut) & 1u);
+              const size_t v0 = lo + ci * chunk, cnt = std::min((size_t)chunk, lo + per - v0);
+              for (int p = 0; p < world; ++p)  // one bulk group: the copies into every rank's destination
+                eng.submit({data[p].data() + v0, out_st.data() + (size_t)so * chunk, cnt, nullptr,
+                            p == world - 1 ? (int)q : -1});
+              if (early_release) {
+                empty_out[so].arrive();
+              } else if (q >= 1) {  // cp.async.bulk.wait_group.read 1: the previous group has read its stage
+                while (eng.groups_read.load(std::memory_order_acquire) < (int)q) std::this_thread::yield();
+                empty_out[(q - 1) % kOut].arrive();
+              }
+            }
+            // cp.async.bulk.wait_group 0: every copy this CTA issued has landed
+            while (eng.taken.load(std::memory_order_acquire) < eng.issued.load(std::memory_order_acquire))
+              std::this_thread::yield();
+          });
+          loader.join();
+          for (auto& x : reducers) x.join();
+          storer.join();
+          eng.stop.store(true, std::memory_order_release);
+          engine.join();
+          if (!barrier(c, bid, deadline, none)) bad.store(1);  // exit: all results have landed everywhere
+          boundary[r].arrive_and_wait(ctas, my_sense);
+          if (bid == 0) {
+            const float tot = (float)(world * (world + 1) / 2);
+            for (size_t i = 0; i < numel; ++i)
+              if (data[r][i] != tot * (float)(i % 5 + 1) + (float)(world * call)) bad.store(2);
+          }
+          boundary[r].arrive_and_wait(ctas, my_sense);
+        }
+      });
+  for (auto& x : th) x.join();
+  return bad.load();
+}

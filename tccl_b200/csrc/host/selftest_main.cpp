@@ -8,12 +8,19 @@ extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds);
 extern "C" int hp_selftest_gemm_rs(int world, int ctas, int tiles_per_owner, int calls);
 extern "C" int hp_selftest_ag(int world, int movers, int consumers, int row_tiles, int calls);
 extern "C" int hp_selftest_push(int world, int calls, int scheme);
+extern "C" int hp_selftest_bulk(int world, int ctas, int chunk, int chunks_per_cta, int calls, int early_release);
 
 int main(int argc, char** argv) {
   if (argc > 2 && std::strcmp(argv[1], "push-broken-variant") == 0) {
     // the size-dependent layout with a per-CTA epoch parity: expected to be reported as a race
     const int rc = hp_selftest_push(std::atoi(argv[2]), 300, 1);
     std::printf("hp_selftest_push(broken variant) -> %d\n", rc);
+    return rc;
+  }
+  if (argc > 2 && std::strcmp(argv[1], "bulk-broken-variant") == 0) {
+    // output stages freed when their copies are issued, not when they have been read: expected to be reported
+    const int rc = hp_selftest_bulk(std::atoi(argv[2]), 2, 4096, 12, 2, 1);
+    std::printf("hp_selftest_bulk(broken variant) -> %d\n", rc);
     return rc;
   }
   const int world = argc > 1 ? std::atoi(argv[1]) : 4;
@@ -30,5 +37,8 @@ int main(int argc, char** argv) {
   if (rc) return rc;
   rc = hp_selftest_push(world, 300, 0);
   std::printf("hp_selftest_push(world=%d) -> %d\n", world, rc);
+  if (rc) return rc;
+  rc = hp_selftest_bulk(world, 2, 48, 7, 2, 0);
+  std::printf("hp_selftest_bulk(world=%d) -> %d\n", world, rc);
   return rc;
 }

@@ -106,3 +106,22 @@ def test_thread_sanitizer_flags_the_size_dependent_push_layout():
     r = subprocess.run([str(exe), "push-broken-variant", "4"], capture_output=True, text=True, timeout=300)
     out = r.stdout + r.stderr
     assert "ThreadSanitizer: data race" in out or r.returncode != 0, out[-2000:]
+
+
+def test_thread_sanitizer_flags_an_output_stage_freed_before_its_copies_have_read_it():
+    """The bulk-copy all-reduce hands its sums to the copy engine from shared-memory stages; a stage
+    may be refilled only when the copies issued from it have READ it (cp.async.bulk.wait_group.read),
+    not when they were issued.  The model keeps the early release as a variant, with a copy-engine
+    thread that runs behind the issuer, so that ThreadSanitizer (or the sum check) is seen to catch
+    it; the order the kernel uses runs clean in test_protocol_is_race_free_under_thread_sanitizer."""
+    import subprocess
+
+    from tccl_b200.utils import build as B
+
+    try:
+        exe = B.build_host_tsan()
+    except RuntimeError as e:
+        pytest.skip(str(e)[:200])
+    r = subprocess.run([str(exe), "bulk-broken-variant", "4"], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert "ThreadSanitizer: data race" in out or r.returncode != 0, out[-2000:]
