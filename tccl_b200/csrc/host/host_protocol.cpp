@@ -795,3 +795,177 @@ extern "C" int hp_selftest_bulk(int world, int ctas, int chunk, int chunks_per_c
   for (auto& x : th) x.join();
   return bad.load();
 }
+
+// ---------------------------------------------------------------------------
+// Model of the barrier-free all-gather -> GEMM on CTA pairs (ag_gemm_pair.cu).  Every CTA of a
+// rank is a mover thread (the epilogue warps: stores its share of the rank's shard into the
+// gathered buffer of the peers, in batches to all ranks or — `ring` — destination by destination,
+// and the CTA that completes a batch raises the row tiles' flags) and a consumer thread (the
+// producer warp: waits for a remote row tile's flag, then reads the rows from the LOCAL gathered
+// buffer).  There is NO entry barrier: the gathered buffer has two halves that alternate on a
+// per-rank count of completed calls, and the ranks run free of each other — a rank may be a call
+// ahead of a peer — while the CTAs of one rank meet at a kernel boundary between calls, as kernels
+// of one stream do.  All buffer accesses are plain: ThreadSanitizer checks the claim that a rank
+// reaches call n+2 (and overwrites the half of call n) only after every peer has finished call n.
+// `mode`: bit 0 = ring-ordered movers; bit 1 = ONE buffer instead of two halves and still no barrier —
+// the mistake the halves are there to prevent, kept so that the sanitizer can be seen to catch it.
+extern "C" int hp_selftest_ag_pair(int world, int ctas, int row_tiles, int calls, int mode) {
+  if (world < 1 || world > TCCL_MAX_WORLD || ctas < 1 || ctas > 16 || row_tiles < 1 || row_tiles > 8) return 100;
+  const int ring = mode & 1;
+  const bool one_buffer = (mode & 2) != 0;
+  constexpr int kRow = 24;
+  const size_t half_elems = (size_t)world * row_tiles * kRow;
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> full(world, std::vector<float>(2 * half_elems, 0.f));
+  std::vector<KernelBoundary> boundary(world);
+  std::atomic<int> bad{0};
+  auto val = [](int call, int src, int rt, int e) { return (float)(call * 10000 + src * 1000 + rt * 50 + e); };
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    for (int b = 0; b < ctas; ++b)
+      th.emplace_back([&, r, b] {
+        HostComm c;
+        c.world = world;
+        c.rank = r;
+        for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+        c.local = local[r].data();
+        c.timeout_ns = 60ull * 1000 * 1000 * 1000;
+        int my_sense = 0;
+        for (int call = 0; call < calls && !bad.load(std::memory_order_relaxed); ++call) {
+          const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+          const uint32_t epoch = A(c.local + TCCL_LOCAL_TILE_EPOCH).load(std::memory_order_relaxed) + 1u;
+          const size_t hoff =
+              one_buffer ? 0 : (size_t)(A(c.local + TCCL_LOCAL_AG_SEQ).load(std::memory_order_relaxed) & 1u) * half_elems;
+          std::thread mover([&] {
+            // groups of (destinations, row tiles) that end in one count + flag raise
+            const int ngroups = ring ? world - 1 : std::min(2, row_tiles);
+            for (int g = 0; g < ngroups; ++g) {
+              const int rt0 = ring ? 0 : g * row_tiles / ngroups, rt1 = ring ? row_tiles : (g + 1) * row_tiles / ngroups;
+              for (int q = 0; q < world; ++q) {
+                if (q == r) continue;  // the own rows are read from the shard
+                if (ring && q != (r + 1 + g) % world) continue;
+                for (int rt = rt0; rt < rt1; ++rt)
+                  for (int e = b; e < kRow; e += ctas)
+                    full[q][hoff + ((size_t)r * row_tiles + rt) * kRow + e] = val(call, r, rt, e);
+              }
+              const uint32_t done = A(c.local + TCCL_LOCAL_AGCNT + g).fetch_add(1u, std::memory_order_acq_rel);
+              if (done == (uint32_t)ctas - 1u) {
+                A(c.local + TCCL_LOCAL_AGCNT + g).store(0u, std::memory_order_relaxed);
+                for (int q = 0; q < world; ++q) {
+                  if (q == r || (ring && q != (r + 1 + g) % world)) continue;
+                  for (int rt = rt0; rt < rt1; ++rt)
+                    A(c.flags[q] + TCCL_FLAG_AG + r * TCCL_MAX_ROW_TILES + rt).store(epoch, std::memory_order_release);
+                }
+              }
+            }
+          });
+          // consumer: this CTA's tiles, the previous rank's rows first (they arrive first in ring order)
+          for (int t = b; t < (world - 1) * row_tiles; t += ctas) {
+            const int j = t / row_tiles, rt = t - j * row_tiles;
+            const int src = ((r - 1 - j) % world + world) % world;
+            if (!wait_reach(c.flags[r] + TCCL_FLAG_AG + src * TCCL_MAX_ROW_TILES + rt, epoch, c, deadline, b, src,
+                            TCCL_W_TILE)) {
+              bad.store(2);
+              break;
+            }
+            for (int e = 0; e < kRow; ++e)
+              if (full[r][hoff + ((size_t)src * row_tiles + rt) * kRow + e] != val(call, src, rt, e)) bad.store(3);
+          }
+          mover.join();
+          const uint32_t done = A(c.local + TCCL_LOCAL_SCHED).fetch_add(1u, std::memory_order_acq_rel);
+          if (done == (uint32_t)ctas - 1u) {
+            A(c.local + TCCL_LOCAL_SCHED).store(0u, std::memory_order_relaxed);
+            A(c.local + TCCL_LOCAL_AG_SEQ).fetch_add(1u, std::memory_order_relaxed);
+            A(c.local + TCCL_LOCAL_TILE_EPOCH).store(epoch, std::memory_order_relaxed);
+          }
+          if ((call & 3) == (r + b) % 4) std::this_thread::yield();  // let the ranks drift apart
+          boundary[r].arrive_and_wait(ctas, my_sense);                // the next kernel of this rank's stream
+        }
+      });
+  for (auto& x : th) x.join();
+  return bad.load();
+}
+
+// ---------------------------------------------------------------------------
+// Model of the barrier-free GEMM -> reduce-scatter on CTA pairs (gemm_rs_pair.cu): every CTA of a
+// rank writes its partial tiles into slot [source][tile] of the OWNER's staging area and raises
+// the tile's flag there; then the CTAs of a rank share out the rank's own tiles (a cursor), wait
+// for the W flags of a tile and sum the W staged partials.  NO entry barrier: the staging area
+// has two halves that alternate on a per-rank count of completed calls; ranks run free of each
+// other, the CTAs of one rank meet at a kernel boundary between calls.  ThreadSanitizer checks the
+// claim that a rank reaches call n+2 (and overwrites the half of call n) only after its call n+1
+// got every peer's partials of call n+1, i.e. after every peer has finished reading call n.
+// `mode` bit 1: ONE half only and still no barrier — the mistake, kept to show the check has teeth.
+extern "C" int hp_selftest_rs_pair(int world, int ctas, int tiles_per_owner, int calls, int mode) {
+  if (world < 1 || world > TCCL_MAX_WORLD || ctas < 1 || ctas > 16 || tiles_per_owner < 1 || tiles_per_owner > 64) return 100;
+  constexpr int kElems = 16;
+  const bool one_half = (mode & 2) != 0;
+  const int tpo = tiles_per_owner;
+  const size_t half_elems = (size_t)world * tpo * kElems;
+  std::vector<std::vector<uint32_t>> flags(world, std::vector<uint32_t>(TCCL_FLAG_WORDS, 0u));
+  std::vector<std::vector<uint32_t>> local(world, std::vector<uint32_t>(TCCL_LOCAL_WORDS, 0u));
+  std::vector<std::vector<float>> stage(world, std::vector<float>(2 * half_elems, 0.f));
+  std::vector<std::vector<float>> out(world, std::vector<float>((size_t)tpo * kElems, 0.f));
+  std::vector<KernelBoundary> boundary(world);
+  std::atomic<int> bad{0};
+  auto partial = [](int call, int src, int owner, int lt, int e) {
+    return (float)(call * 1000 + src * 100 + owner * 10 + (lt * 3 + e) % 7);
+  };
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    for (int b = 0; b < ctas; ++b)
+      th.emplace_back([&, r, b] {
+        HostComm c;
+        c.world = world;
+        c.rank = r;
+        for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
+        c.local = local[r].data();
+        c.timeout_ns = 60ull * 1000 * 1000 * 1000;
+        int my_sense = 0;
+        for (int call = 0; call < calls && !bad.load(std::memory_order_relaxed); ++call) {
+          const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
+          const uint32_t epoch = A(c.local + TCCL_LOCAL_TILE_EPOCH).load(std::memory_order_relaxed) + 1u;
+          const size_t hoff =
+              one_half ? 0 : (size_t)(A(c.local + TCCL_LOCAL_RS_SEQ).load(std::memory_order_relaxed) & 1u) * half_elems;
+          // mainloop + epilogue: this CTA's tiles, owners in turn (peers first, own rows last)
+          for (int t = b; t < world * tpo; t += ctas) {
+            const int lt = t / world, owner = (r + 1 + t % world) % world;
+            float* slot = stage[owner].data() + hoff + ((size_t)r * tpo + lt) * kElems;
+            for (int e = 0; e < kElems; ++e) slot[e] = partial(call, r, owner, lt, e);
+            A(c.flags[owner] + TCCL_FLAG_TILE + r * TCCL_MAX_TILES + lt).store(epoch, std::memory_order_release);
+          }
+          // final reduction of the rank's own tiles, shared out over its CTAs
+          for (;;) {
+            const uint32_t u = A(c.local + TCCL_LOCAL_RS_NEXT).fetch_add(1u, std::memory_order_acq_rel);
+            if (u >= (uint32_t)tpo) break;
+            bool ok = true;
+            for (int src = 0; src < world && ok; ++src)
+              ok = wait_reach(c.flags[r] + TCCL_FLAG_TILE + src * TCCL_MAX_TILES + u, epoch, c, deadline, b, src, TCCL_W_TILE);
+            if (!ok) {
+              bad.store(2);
+              break;
+            }
+            for (int e = 0; e < kElems; ++e) {
+              float s = 0.f, want = 0.f;
+              for (int src = 0; src < world; ++src) {
+                s += stage[r][hoff + ((size_t)src * tpo + u) * kElems + e];
+                want += partial(call, src, r, (int)u, e);
+              }
+              out[r][(size_t)u * kElems + e] = s;
+              if (s != want) bad.store(3);
+            }
+          }
+          boundary[r].arrive_and_wait(ctas, my_sense);  // every CTA of the rank has left its final loop
+          if (b == 0) {  // what the last CTA of the kernel does
+            A(c.local + TCCL_LOCAL_RS_NEXT).store(0u, std::memory_order_relaxed);
+            A(c.local + TCCL_LOCAL_RS_SEQ).fetch_add(1u, std::memory_order_relaxed);
+            A(c.local + TCCL_LOCAL_TILE_EPOCH).store(epoch, std::memory_order_relaxed);
+          }
+          if ((call & 3) == (r + b) % 4) std::this_thread::yield();  // let the ranks drift apart
+          boundary[r].arrive_and_wait(ctas, my_sense);  // the next kernel of this rank's stream
+        }
+      });
+  for (auto& x : th) x.join();
+  return bad.load();
+}

@@ -8,6 +8,8 @@ extern "C" int hp_selftest_threads(int world, int numel, int chunk, int rounds);
 extern "C" int hp_selftest_gemm_rs(int world, int ctas, int tiles_per_owner, int calls);
 extern "C" int hp_selftest_ag(int world, int movers, int consumers, int row_tiles, int calls);
 extern "C" int hp_selftest_push(int world, int calls, int scheme);
+extern "C" int hp_selftest_ag_pair(int world, int ctas, int row_tiles, int calls, int mode);
+extern "C" int hp_selftest_rs_pair(int world, int ctas, int tiles_per_owner, int calls, int mode);
 extern "C" int hp_selftest_bulk(int world, int ctas, int chunk, int chunks_per_cta, int calls, int early_release);
 
 int main(int argc, char** argv) {
@@ -15,6 +17,18 @@ int main(int argc, char** argv) {
     // the size-dependent layout with a per-CTA epoch parity: expected to be reported as a race
     const int rc = hp_selftest_push(std::atoi(argv[2]), 300, 1);
     std::printf("hp_selftest_push(broken variant) -> %d\n", rc);
+    return rc;
+  }
+  if (argc > 2 && std::strcmp(argv[1], "ag-pair-broken-variant") == 0) {
+    // one gathered buffer, no halves, no barrier: a rank one call ahead overwrites rows a peer still reads
+    const int rc = hp_selftest_ag_pair(std::atoi(argv[2]), 3, 4, 200, 2);
+    std::printf("hp_selftest_ag_pair(broken variant) -> %d\n", rc);
+    return rc;
+  }
+  if (argc > 2 && std::strcmp(argv[1], "rs-pair-broken-variant") == 0) {
+    // one staging half, no barrier: a rank one call ahead overwrites partials a peer is still summing
+    const int rc = hp_selftest_rs_pair(std::atoi(argv[2]), 3, 5, 200, 2);
+    std::printf("hp_selftest_rs_pair(broken variant) -> %d\n", rc);
     return rc;
   }
   if (argc > 2 && std::strcmp(argv[1], "bulk-broken-variant") == 0) {
@@ -37,6 +51,14 @@ int main(int argc, char** argv) {
   if (rc) return rc;
   rc = hp_selftest_push(world, 300, 0);
   std::printf("hp_selftest_push(world=%d) -> %d\n", world, rc);
+  if (rc) return rc;
+  for (int ring = 0; ring < 2; ++ring) {
+    rc = hp_selftest_ag_pair(world, 3, 4, 40, ring);
+    std::printf("hp_selftest_ag_pair(world=%d, ring=%d) -> %d\n", world, ring, rc);
+    if (rc) return rc;
+  }
+  rc = hp_selftest_rs_pair(world, 3, 5, 40, 0);
+  std::printf("hp_selftest_rs_pair(world=%d) -> %d\n", world, rc);
   if (rc) return rc;
   rc = hp_selftest_bulk(world, 2, 48, 7, 2, 0);
   std::printf("hp_selftest_bulk(world=%d) -> %d\n", world, rc);

@@ -73,8 +73,11 @@ def test_rank_that_stops_mid_all_reduce(pull_down):
 def test_protocol_is_race_free_under_thread_sanitizer(W):
     """Ranks (and CTAs) as threads of one process, instrumented with ThreadSanitizer: every plain
     access of the data buffers must be ordered by the release/acquire flags.  Covers the barrier,
-    the double-tree pipeline, the GEMM -> reduce-scatter tile flags (deferred release, final phase,
-    epoch hand-over across calls) and the all-gather -> GEMM arrival flags."""
+    the double-tree pipeline (pushed and pulled way down), the GEMM -> reduce-scatter tile flags
+    (deferred release, final phase, epoch hand-over across calls), the all-gather -> GEMM arrival
+    flags, the push all-reduce with changing sizes and grids, the barrier-free CTA-pair forms of both
+    fused GEMM ops (two alternating halves, 40 calls with the ranks drifting apart; batched and
+    ring-ordered movers) and the stage pipeline of the bulk-copy all-reduce."""
     import subprocess
 
     from tccl_b200.utils import build as B
@@ -123,5 +126,42 @@ def test_thread_sanitizer_flags_an_output_stage_freed_before_its_copies_have_rea
     except RuntimeError as e:
         pytest.skip(str(e)[:200])
     r = subprocess.run([str(exe), "bulk-broken-variant", "4"], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert "ThreadSanitizer: data race" in out or r.returncode != 0, out[-2000:]
+
+
+def test_thread_sanitizer_flags_a_single_gather_buffer_without_a_barrier():
+    """The all-gather -> GEMM pair kernel has no entry barrier because its gathered buffer has two
+    halves that alternate from call to call; with ONE buffer a rank that is a call ahead overwrites
+    rows a slower peer is still reading.  The model keeps that variant so that ThreadSanitizer (or the
+    value check) is seen to catch it; the two-halves scheme runs clean, with batched and with
+    ring-ordered movers, in test_protocol_is_race_free_under_thread_sanitizer."""
+    import subprocess
+
+    from tccl_b200.utils import build as B
+
+    try:
+        exe = B.build_host_tsan()
+    except RuntimeError as e:
+        pytest.skip(str(e)[:200])
+    r = subprocess.run([str(exe), "ag-pair-broken-variant", "4"], capture_output=True, text=True, timeout=300)
+    out = r.stdout + r.stderr
+    assert "ThreadSanitizer: data race" in out or r.returncode != 0, out[-2000:]
+
+
+def test_thread_sanitizer_flags_a_single_staging_half_without_a_barrier():
+    """Same obligation for the GEMM -> reduce-scatter pair kernel: its staging area alternates between
+    two halves instead of opening with a barrier; with ONE half a rank that is a call ahead overwrites
+    partials a slower peer is still summing.  The kept variant must be caught; the two-halves scheme
+    runs clean in test_protocol_is_race_free_under_thread_sanitizer (40 calls, ranks drifting apart)."""
+    import subprocess
+
+    from tccl_b200.utils import build as B
+
+    try:
+        exe = B.build_host_tsan()
+    except RuntimeError as e:
+        pytest.skip(str(e)[:200])
+    r = subprocess.run([str(exe), "rs-pair-broken-variant", "4"], capture_output=True, text=True, timeout=300)
     out = r.stdout + r.stderr
     assert "ThreadSanitizer: data race" in out or r.returncode != 0, out[-2000:]
