@@ -533,13 +533,18 @@ namespace {
 struct KernelBoundary {  // sense-reversing barrier among the CTA threads of one rank
   std::atomic<int> count{0};
   std::atomic<int> sense{0};
-  void arrive_and_wait(int n, int& my_sense) {
+  // `stop`: once it is non-zero (a check failed somewhere) nobody waits any more — a thread that has left its
+  // call loop must not leave the others stuck here
+  void arrive_and_wait(int n, int& my_sense, const std::atomic<int>* stop = nullptr) {
     my_sense ^= 1;
     if (count.fetch_add(1, std::memory_order_acq_rel) == n - 1) {
       count.store(0, std::memory_order_relaxed);
       sense.store(my_sense, std::memory_order_release);
     } else {
-      while (sense.load(std::memory_order_acquire) != my_sense) std::this_thread::yield();
+      while (sense.load(std::memory_order_acquire) != my_sense) {
+        if (stop && stop->load(std::memory_order_relaxed)) return;
+        std::this_thread::yield();
+      }
     }
   }
 };
@@ -830,7 +835,7 @@ extern "C" int hp_selftest_ag_pair(int world, int ctas, int row_tiles, int calls
         c.rank = r;
         for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
         c.local = local[r].data();
-        c.timeout_ns = 60ull * 1000 * 1000 * 1000;
+        c.timeout_ns = 8ull * 1000 * 1000 * 1000;
         int my_sense = 0;
         for (int call = 0; call < calls && !bad.load(std::memory_order_relaxed); ++call) {
           const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
@@ -880,7 +885,7 @@ extern "C" int hp_selftest_ag_pair(int world, int ctas, int row_tiles, int calls
             A(c.local + TCCL_LOCAL_TILE_EPOCH).store(epoch, std::memory_order_relaxed);
           }
           if ((call & 3) == (r + b) % 4) std::this_thread::yield();  // let the ranks drift apart
-          boundary[r].arrive_and_wait(ctas, my_sense);                // the next kernel of this rank's stream
+          boundary[r].arrive_and_wait(ctas, my_sense, &bad);          // the next kernel of this rank's stream
         }
       });
   for (auto& x : th) x.join();
@@ -921,7 +926,7 @@ extern "C" int hp_selftest_rs_pair(int world, int ctas, int tiles_per_owner, int
         c.rank = r;
         for (int p = 0; p < TCCL_MAX_WORLD; ++p) c.flags[p] = p < world ? flags[p].data() : nullptr;
         c.local = local[r].data();
-        c.timeout_ns = 60ull * 1000 * 1000 * 1000;
+        c.timeout_ns = 8ull * 1000 * 1000 * 1000;
         int my_sense = 0;
         for (int call = 0; call < calls && !bad.load(std::memory_order_relaxed); ++call) {
           const auto deadline = clk::now() + std::chrono::nanoseconds(c.timeout_ns);
@@ -956,14 +961,15 @@ extern "C" int hp_selftest_rs_pair(int world, int ctas, int tiles_per_owner, int
               if (s != want) bad.store(3);
             }
           }
-          boundary[r].arrive_and_wait(ctas, my_sense);  // every CTA of the rank has left its final loop
+          boundary[r].arrive_and_wait(ctas, my_sense, &bad);  // every CTA of the rank has left its final loop
+          if (bad.load(std::memory_order_relaxed)) break;
           if (b == 0) {  // what the last CTA of the kernel does
             A(c.local + TCCL_LOCAL_RS_NEXT).store(0u, std::memory_order_relaxed);
             A(c.local + TCCL_LOCAL_RS_SEQ).fetch_add(1u, std::memory_order_relaxed);
             A(c.local + TCCL_LOCAL_TILE_EPOCH).store(epoch, std::memory_order_relaxed);
           }
           if ((call & 3) == (r + b) % 4) std::this_thread::yield();  // let the ranks drift apart
-          boundary[r].arrive_and_wait(ctas, my_sense);  // the next kernel of this rank's stream
+          boundary[r].arrive_and_wait(ctas, my_sense, &bad);  // the next kernel of this rank's stream
         }
       });
   for (auto& x : th) x.join();
