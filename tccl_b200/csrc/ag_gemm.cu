@@ -15,6 +15,10 @@
 // Flags carry the call's epoch (the same device-resident epoch the GEMM ->
 // reduce-scatter kernel uses; the last CTA to finish advances it), so nothing is
 // ever reset and stale flags of earlier calls can never satisfy a wait.
+//
+// The reference has no kernel of this kind: fusing a matmul with its collective is the goal its
+// presentation names (presentation.pdf, slide 4: "fusing (matmul-allreduce) for overlap"); its collectives
+// are stand-alone Triton kernels (triton_reduce_scatter.py:59-127, triton_all_gather.py:32-95).
 #include "gemm_host.cuh"
 #include "gemm_tcgen05.cuh"
 

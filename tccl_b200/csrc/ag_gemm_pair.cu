@@ -22,6 +22,10 @@
 //    call n+2 only after its call n+1 consumed every peer's rows of call n+1,
 //    i.e. after every peer has finished call n and stopped reading the half that
 //    is being overwritten.  A caller-provided buffer keeps the barrier.
+//
+// The reference has no kernel of this kind: fusing a matmul with its collective is the goal its
+// presentation names (presentation.pdf, slide 4: "fusing (matmul-allreduce) for overlap"); its collectives
+// are stand-alone Triton kernels (triton_reduce_scatter.py:59-127, triton_all_gather.py:32-95).
 #include "gemm_host.cuh"
 #include "gemm_tcgen05_2cta.cuh"
 

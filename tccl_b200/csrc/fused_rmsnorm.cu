@@ -9,6 +9,9 @@
 // activations never make an extra trip through HBM, and the unfused sequence
 // (all-reduce kernel, then an elementwise kernel, then a norm kernel) collapses
 // into one launch with one entry and one exit barrier.
+//
+// The reference's all-reduce is a stand-alone one-shot kernel (triton_one_shot_all_reduce_no_128.py:35-96);
+// fusing collectives with the compute around them is the goal its presentation names (presentation.pdf, slide 4).
 #include "common.cuh"
 
 namespace tccl {

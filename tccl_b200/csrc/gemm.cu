@@ -2,6 +2,7 @@
 // host-side TMA descriptor helper shared with the fused kernels.  Used to
 // validate and time the mainloop by itself; plain library-GEMM work would go to
 // cuBLAS, the point of this kernel is to be the body the collectives fuse into.
+// The reference has no GEMM (presentation.pdf, slide 4, names the fusion with one as a goal).
 #include "gemm_host.cuh"
 #include "gemm_tcgen05.cuh"
 

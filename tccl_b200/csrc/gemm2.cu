@@ -1,5 +1,6 @@
 // Stand-alone bf16 GEMM on the CTA-pair mainloop (gemm_tcgen05_2cta.cuh):
 // C = A * Bt^T with 256 x 256 tiles per pair of SMs, persistent over the tiles.
+// The reference has no GEMM (presentation.pdf, slide 4, names the fusion with one as a goal).
 #include "gemm_host.cuh"
 #include "gemm_tcgen05_2cta.cuh"
 

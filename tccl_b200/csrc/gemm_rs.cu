@@ -19,6 +19,10 @@
 // CTA to finish), so nothing has to be reset and a captured graph can replay.
 // The entry barrier keeps a fast rank from overwriting a staging slot that a
 // slow rank is still reducing from the previous call.
+//
+// The reference has no kernel of this kind: fusing a matmul with its collective is the goal its
+// presentation names (presentation.pdf, slide 4: "fusing (matmul-allreduce) for overlap"); its collectives
+// are stand-alone Triton kernels (triton_reduce_scatter.py:59-127, triton_all_gather.py:32-95).
 #include "gemm_host.cuh"
 #include "gemm_tcgen05.cuh"
 

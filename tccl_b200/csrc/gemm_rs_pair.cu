@@ -29,6 +29,10 @@
 //    (TCCL_RS_SYNC_ENTRY).
 // Flags carry the epoch shared by the fused GEMM kernels (TCCL_LOCAL_TILE_EPOCH);
 // nothing is ever reset.
+//
+// The reference has no kernel of this kind: fusing a matmul with its collective is the goal its
+// presentation names (presentation.pdf, slide 4: "fusing (matmul-allreduce) for overlap"); its collectives
+// are stand-alone Triton kernels (triton_reduce_scatter.py:59-127, triton_all_gather.py:32-95).
 #include "gemm_host.cuh"
 #include "gemm_tcgen05_2cta.cuh"
 

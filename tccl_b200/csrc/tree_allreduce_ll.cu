@@ -24,6 +24,9 @@
 //
 // The sums reach every rank through the down slots, so no user tensor has to be
 // symmetric here: the input is read and the result written by their owner only.
+//
+// Same trees and the same "two sends and two receives per GPU" as the algorithm the reference intends
+// (triton_double_tree_allreduce.py:227-335, tree.py:36-51); its own kernel never completes a reduction.
 #include "common.cuh"
 
 namespace tccl {

@@ -1,7 +1,7 @@
 """Tensor-parallel Llama-style MLP block built on the fused kernels.
 
 The reference ships no model; "fuse collectives with matmuls" is the stated
-motivation of the project (slide 4).  This block is that use case, with
+motivation of the project (``presentation.pdf``, slide 4).  This block is that use case, with
 Llama-3-8B dimensions as the default (hidden 4096, intermediate 14336):
 
 * sequence-parallel form (``forward``): the input is this rank's token shard

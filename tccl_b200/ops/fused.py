@@ -1,6 +1,6 @@
 """Fused compute + collective ops for tensor parallelism (the "extensible
-collectives" the reference names as its motivation on slide 4 but does not
-implement): GEMM -> reduce-scatter, all-gather -> GEMM, and all-reduce + bias +
+collectives" the reference names as its motivation — ``presentation.pdf``, slide 4
+— but does not implement): GEMM -> reduce-scatter, all-gather -> GEMM, and all-reduce + bias +
 residual + RMSNorm.  Each is ONE kernel in which the tensor-core tiles
 (tcgen05 / TMEM, fed by TMA from local memory) and the peer traffic (P2P or
 NVLS stores / loads over NVLink) overlap tile by tile.

@@ -1,6 +1,7 @@
 """Stand-alone tcgen05 GEMM (``c = a @ bt.T``), the mainloop the fused
 collective kernels are built on.  bf16 operands, fp32 accumulation in tensor
-memory, bf16 result."""
+memory, bf16 result.  The reference has no GEMM; ``presentation.pdf`` (slide 4) names
+the fusion of a matmul with its collective as the goal this mainloop serves."""
 from __future__ import annotations
 
 import ctypes as C
