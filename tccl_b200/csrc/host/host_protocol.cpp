@@ -975,3 +975,155 @@ extern "C" int hp_selftest_rs_pair(int world, int ctas, int tiles_per_owner, int
   for (auto& x : th) x.join();
   return bad.load();
 }
+
+// ---------------------------------------------------------------------------
+// Model of the flag-in-line double tree (tree_allreduce_ll.cu): every line on the wire is
+// {payload, call number} twice, written and polled as two 8-byte halves (the unit that arrives
+// whole); there are no counters and no acknowledgements, only slots [tree][left | right |
+// down][call mod depth] per rank.  Ranks run free of each other over many calls (the four role
+// threads of a rank meet between calls, as the CTAs of consecutive kernels do); the sums are
+// checked after every call.  What this exercises is the numbering: a rank that is a call ahead
+// writes the NEXT slot, and a slot comes round again only when its lines have long been read —
+// `depth` = 1 is accepted too and must still give the right sums, because a rank cannot finish
+// call n before every rank has contributed to call n.
+extern "C" int hp_selftest_tree_ll(int world, int numel, int calls, int depth) {
+  if (world < 1 || world > TCCL_MAX_WORLD || numel < 2 || (numel & 1) || depth < 1 || depth > 8) return 100;
+  const int lines = numel / 2;                  // two floats of payload per line
+  const int half0 = (lines + 1) / 2;            // tree 0 takes the first half of the lines, tree 1 the rest
+  using Half = std::atomic<uint64_t>;
+  // slot(rank, tree, which, seq) -> 2 * lines halves
+  const size_t slot_halves = (size_t)2 * lines;
+  std::vector<std::vector<Half>> ll(world);
+  for (auto& v : ll) v = std::vector<Half>((size_t)2 * 3 * depth * slot_halves);
+  for (auto& v : ll)
+    for (auto& h : v) h.store(0, std::memory_order_relaxed);
+  auto slot = [&](int rank, int tree, int which, uint32_t seq) {
+    return ll[rank].data() + ((size_t)(tree * 3 + which) * depth + seq % depth) * slot_halves;
+  };
+  std::vector<std::vector<float>> in(world, std::vector<float>(numel)), out(world, std::vector<float>(numel, 0.f));
+  std::vector<KernelBoundary> boundary(world);
+  std::atomic<int> bad{0};
+  auto nbr = [&](int N, int r, int tree, int* parent, int* left, int* right) {
+    auto a = [&](int rr, int* p, int* l, int* rt) {
+      *p = *l = *rt = -1;
+      if (N == 1) return;
+      if (rr == 0) {
+        int top = 1;
+        while (top * 2 <= N - 1) top *= 2;
+        *l = top;
+        return;
+      }
+      const int s = rr & -rr;
+      int up = (rr ^ s) | (s << 1);
+      if (up >= N) up = rr ^ s;
+      *p = up;
+      if (s == 1) return;
+      *l = rr - (s >> 1);
+      int step = s >> 1, x = rr + step;
+      while (x >= N && step > 1) {
+        step >>= 1;
+        x = rr + step;
+      }
+      *rt = x >= N ? -1 : x;
+    };
+    if (tree == 0) return a(r, parent, left, right);
+    a((r + 1) % N, parent, left, right);
+    auto back = [&](int x) { return x < 0 ? -1 : (x - 1 + N) % N; };
+    *parent = back(*parent);
+    *left = back(*left);
+    *right = back(*right);
+  };
+  auto pack = [](float d, uint32_t flag) {
+    uint32_t u;
+    std::memcpy(&u, &d, 4);
+    return (uint64_t)u | ((uint64_t)flag << 32);
+  };
+  const auto t_end = clk::now() + std::chrono::seconds(60);
+  // polls one line until both halves carry `flag`; false when the time is up or a check failed elsewhere
+  auto get = [&](Half* line, uint32_t flag, float* d0, float* d1) {
+    for (;;) {
+      const uint64_t a = line[0].load(std::memory_order_relaxed), b = line[1].load(std::memory_order_relaxed);
+      if ((uint32_t)(a >> 32) == flag && (uint32_t)(b >> 32) == flag) {
+        const uint32_t ua = (uint32_t)a, ub = (uint32_t)b;
+        std::memcpy(d0, &ua, 4);
+        std::memcpy(d1, &ub, 4);
+        return true;
+      }
+      if (bad.load(std::memory_order_relaxed) || clk::now() > t_end) return false;
+      std::this_thread::yield();
+    }
+  };
+  auto put = [&](Half* line, float d0, float d1, uint32_t flag) {
+    line[0].store(pack(d0, flag), std::memory_order_relaxed);
+    line[1].store(pack(d1, flag), std::memory_order_relaxed);
+  };
+  std::vector<std::thread> th;
+  for (int r = 0; r < world; ++r)
+    for (int role = 0; role < 4; ++role)
+      th.emplace_back([&, r, role] {
+        const int tree = role & 1;
+        const bool is_up = role < 2;
+        int parent, left, right;
+        nbr(world, r, tree, &parent, &left, &right);
+        int cslot = 0;
+        if (parent >= 0) {
+          int pp, pl, pr;
+          nbr(world, parent, tree, &pp, &pl, &pr);
+          cslot = pl == r ? 0 : 1;
+        }
+        const int lo = tree ? half0 : 0, n = tree ? lines - half0 : half0;
+        int my_sense = 0;
+        for (int call = 0; call < calls && !bad.load(std::memory_order_relaxed); ++call) {
+          if (role == 0)  // the rank's "host" writes the input between two kernels
+            for (int i = 0; i < numel; ++i) in[r][i] = (float)((r + 1) * (i % 5 + 1) + call);
+          boundary[r].arrive_and_wait(4, my_sense, &bad);
+          const uint32_t g = (uint32_t)call, flag = g + 1u;  // every pipeline counts its own calls: here they agree
+          bool ok = true;
+          if (is_up) {
+            for (int i = 0; i < n && ok; ++i) {
+              float d0 = in[r][2 * (lo + i)], d1 = in[r][2 * (lo + i) + 1], x0, x1;
+              if (left >= 0) {
+                ok = get(slot(r, tree, 0, g) + 2 * i, flag, &x0, &x1);
+                d0 += x0;
+                d1 += x1;
+                if (ok && right >= 0) {
+                  ok = get(slot(r, tree, 1, g) + 2 * i, flag, &x0, &x1);
+                  d0 += x0;
+                  d1 += x1;
+                }
+              }
+              if (!ok) break;
+              if (parent >= 0) {
+                put(slot(parent, tree, cslot, g) + 2 * i, d0, d1, flag);
+              } else {
+                if (left >= 0) put(slot(left, tree, 2, g) + 2 * i, d0, d1, flag);
+                if (right >= 0) put(slot(right, tree, 2, g) + 2 * i, d0, d1, flag);
+                out[r][2 * (lo + i)] = d0;
+                out[r][2 * (lo + i) + 1] = d1;
+              }
+            }
+          } else if (parent >= 0) {
+            for (int i = 0; i < n && ok; ++i) {
+              float d0, d1;
+              ok = get(slot(r, tree, 2, g) + 2 * i, flag, &d0, &d1);
+              if (!ok) break;
+              if (left >= 0) put(slot(left, tree, 2, g) + 2 * i, d0, d1, flag);
+              if (right >= 0) put(slot(right, tree, 2, g) + 2 * i, d0, d1, flag);
+              out[r][2 * (lo + i)] = d0;
+              out[r][2 * (lo + i) + 1] = d1;
+            }
+          }
+          if (!ok) bad.store(1);
+          if ((call & 3) == (r + role) % 4) std::this_thread::yield();  // let the ranks drift apart
+          boundary[r].arrive_and_wait(4, my_sense, &bad);
+          if (role == 0 && !bad.load(std::memory_order_relaxed)) {
+            const float tot = (float)(world * (world + 1) / 2);
+            for (int i = 0; i < numel; ++i)
+              if (out[r][i] != tot * (float)(i % 5 + 1) + (float)(world * call)) bad.store(2);
+          }
+          boundary[r].arrive_and_wait(4, my_sense, &bad);
+        }
+      });
+  for (auto& x : th) x.join();
+  return bad.load();
+}

@@ -10,6 +10,7 @@ extern "C" int hp_selftest_ag(int world, int movers, int consumers, int row_tile
 extern "C" int hp_selftest_push(int world, int calls, int scheme);
 extern "C" int hp_selftest_ag_pair(int world, int ctas, int row_tiles, int calls, int mode);
 extern "C" int hp_selftest_rs_pair(int world, int ctas, int tiles_per_owner, int calls, int mode);
+extern "C" int hp_selftest_tree_ll(int world, int numel, int calls, int depth);
 extern "C" int hp_selftest_bulk(int world, int ctas, int chunk, int chunks_per_cta, int calls, int early_release);
 
 int main(int argc, char** argv) {
@@ -55,6 +56,11 @@ int main(int argc, char** argv) {
   for (int ring = 0; ring < 2; ++ring) {
     rc = hp_selftest_ag_pair(world, 3, 4, 40, ring);
     std::printf("hp_selftest_ag_pair(world=%d, ring=%d) -> %d\n", world, ring, rc);
+    if (rc) return rc;
+  }
+  for (int depth = 1; depth <= 4; depth += 3) {
+    rc = hp_selftest_tree_ll(world, 194, 60, depth);
+    std::printf("hp_selftest_tree_ll(world=%d, depth=%d) -> %d\n", world, depth, rc);
     if (rc) return rc;
   }
   rc = hp_selftest_rs_pair(world, 3, 5, 40, 0);

@@ -73,7 +73,8 @@ def test_rank_that_stops_mid_all_reduce(pull_down):
 def test_protocol_is_race_free_under_thread_sanitizer(W):
     """Ranks (and CTAs) as threads of one process, instrumented with ThreadSanitizer: every plain
     access of the data buffers must be ordered by the release/acquire flags.  Covers the barrier,
-    the double-tree pipeline (pushed and pulled way down), the GEMM -> reduce-scatter tile flags
+    the double-tree pipeline (pushed and pulled way down), the flag-in-line tree (slot depth 4 and 1),
+    the GEMM -> reduce-scatter tile flags
     (deferred release, final phase, epoch hand-over across calls), the all-gather -> GEMM arrival
     flags, the push all-reduce with changing sizes and grids, the barrier-free CTA-pair forms of both
     fused GEMM ops (two alternating halves, 40 calls with the ranks drifting apart; batched and
